@@ -36,7 +36,8 @@ class LayerCache:
     k: Optional[torch.Tensor] = None         # [pages + 1, kv_heads, page_size, head_dim]
     v: Optional[torch.Tensor] = None
     writes: bool = True                      # False: this entry reads another entry's pages
-    state: Optional[torch.Tensor] = None     # [slots + 1, *state_shape]; slot 0 is the sink
+    state: Optional[torch.Tensor] = None     # the mixer's state, [slots + 1, *state_shape]; slot 0 is the sink
+    states: Dict[str, torch.Tensor] = field(default_factory=dict)   # states of the block itself, by name, same layout
 
 
 @dataclass
@@ -52,7 +53,8 @@ class GroupPlan:
 class CachePlan:
     groups: List[GroupPlan]
     group_of_entry: Dict[int, int]        # every run-list entry with a paged cache (owned or read)
-    state_entries: Dict[int, object]      # run-list entry -> StateSpec
+    state_entries: Dict[int, object]      # run-list entry -> StateSpec of its mixer
+    block_states: Dict[int, Dict[str, object]] = field(default_factory=dict)   # run-list entry -> name -> StateSpec
 
 
 def plan_cache(model, page_size: int, itemsize: int) -> CachePlan:
@@ -60,11 +62,16 @@ def plan_cache(model, page_size: int, itemsize: int) -> CachePlan:
     by_need: Dict[Optional[int], int] = {}
     group_of_entry: Dict[int, int] = {}
     state_entries: Dict[int, object] = {}
+    block_states: Dict[int, Dict[str, object]] = {}
     for e, entry in enumerate(model.run_list):
-        mixer = model.blocks[entry.layer].mixer
+        block = model.blocks[entry.layer]
+        mixer = block.mixer
         state = mixer.state_spec()
         if state is not None:
             state_entries[e] = state
+        own = getattr(block, "state_specs", None)
+        if own is not None and own():
+            block_states[e] = dict(own())
         kv = mixer.cache_spec()
         if kv is None:
             continue
@@ -77,9 +84,9 @@ def plan_cache(model, page_size: int, itemsize: int) -> CachePlan:
             groups.append(GroupPlan(need, page_size))
         g = by_need[need]
         groups[g].entries.append(e)
-        groups[g].bytes_per_page += 2 * page_size * kv.num_kv_heads * kv.head_dim * itemsize
+        groups[g].bytes_per_page += page_size * kv.num_kv_heads * (kv.head_dim + (kv.v_head_dim or kv.head_dim)) * itemsize
         group_of_entry[e] = g
-    return CachePlan(groups, group_of_entry, state_entries)
+    return CachePlan(groups, group_of_entry, state_entries, block_states)
 
 
 def cache_budget_bytes(free: int, total: int, memory_ratio: float) -> int:
@@ -148,7 +155,7 @@ class PagedCache:
                 if entry.reads is None:
                     shape = (plan.groups[g].num_pages + 1, kv.num_kv_heads, plan.groups[g].page_size, kv.head_dim)
                     cache.k = torch.zeros(shape, dtype=dtype, device=device)
-                    cache.v = torch.zeros(shape, dtype=dtype, device=device)
+                    cache.v = torch.zeros(shape[:3] + (kv.v_head_dim or kv.head_dim,), dtype=dtype, device=device)
                     owned[e] = cache
                 else:
                     cache.k, cache.v, cache.writes = owned[entry.reads].k, owned[entry.reads].v, False
@@ -156,6 +163,9 @@ class PagedCache:
             if state is not None:
                 cache.state = torch.zeros((max_requests + 1,) + tuple(state.shape), dtype=state.dtype,
                                           device=device)
+            for name, spec in plan.block_states.get(e, {}).items():
+                cache.states[name] = torch.zeros((max_requests + 1,) + tuple(spec.shape), dtype=spec.dtype,
+                                                 device=device)
             self.layer_caches.append(cache)
 
     def bytes(self) -> int:
@@ -165,4 +175,6 @@ class PagedCache:
                 total += 2 * c.k.numel() * c.k.element_size()
             if c.state is not None:
                 total += c.state.numel() * c.state.element_size()
+            for t in c.states.values():
+                total += t.numel() * t.element_size()
         return total

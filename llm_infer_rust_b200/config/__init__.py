@@ -2,7 +2,8 @@ from .spec import ConfigError, LayerSpec, ModelSpec, PartSpec, RunEntry
 from .registry import (Architecture, register_architecture, registered_architectures,
                        resolve_architecture)
 from .qwen3 import Qwen3Config
+from .kefetar import KefetarConfig
 
 __all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "RunEntry", "Architecture",
            "register_architecture", "registered_architectures", "resolve_architecture",
-           "Qwen3Config"]
+           "Qwen3Config", "KefetarConfig"]

@@ -8,7 +8,7 @@ run time: ``register_architecture`` is all that a new architecture needs.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, List, Sequence
+from typing import Any, Callable, Dict, List, Optional, Sequence
 
 from .spec import ConfigError, ModelSpec
 
@@ -16,7 +16,7 @@ from .spec import ConfigError, ModelSpec
 @dataclass(frozen=True)
 class Architecture:
     name: str                                     # e.g. "Qwen3ForCausalLM"
-    model_type: str                               # config.json "model_type"
+    model_type: Optional[str]                     # config.json "model_type" (None: the architecture's files have none)
     parse_config: Callable[[dict], Any]           # raw config.json -> typed configuration
     model_spec: Callable[[Any], ModelSpec]        # typed configuration -> parts and run list
     weight_plan: Callable[[Any], List[Any]]       # typed configuration -> WeightBinding list
@@ -43,6 +43,8 @@ def resolve_architecture(raw_config: dict) -> Architecture:
     if not isinstance(raw_config, dict):
         raise ConfigError("config must be an object")
     names = raw_config.get("architectures")
+    if names is None and isinstance(raw_config.get("architecture"), str):
+        names = [raw_config["architecture"]]          # a file that names its one architecture as a string
     model_type = raw_config.get("model_type")
     if not isinstance(names, list) or not names or not (model_type is None or isinstance(model_type, str)):
         raise ConfigError("config.json needs a non-empty architectures list (and model_type, a string)")

@@ -6,7 +6,9 @@
 // tensor-core kernels.  The real head size `hd` (any even number up to HEAD_DIM; the
 // reference's configuration allows every even head size: src/models/qwen3/config.rs:160-162)
 // is a run-time argument: rows of q, the cache and the output are `hd` wide, the tiles
-// in shared memory HEAD_DIM wide with zeros beyond `hd`.
+// in shared memory HEAD_DIM wide with zeros beyond `hd`.  Values may have a width of their own (`hd_v`, rows of
+// the value cache and of the output; HEAD_DIM covers the wider of the two), and a score may be soft-capped:
+// s <- cap * tanh(s / cap) after the scale and before the mask (cap <= 0: no cap).
 //
 // Semantics (reference: src/models/attention/backend.rs:1455-1498): query head h
 // reads KV head h / (nh / nkv); score = q.k / sqrt(d) (the scale is a
@@ -71,7 +73,7 @@ struct VecState {
 template <typename T>
 __device__ __forceinline__ void warp_key_block(const T* ks, const T* vs, const float* qs, const int* qpos,
                                                int first_key, int kv_end, int window, VecState& st,
-                                               float* ps) {
+                                               float* ps, float softcap) {
   using G = RowGeom<T>;
   const int lane = threadIdx.x & 31;
   float s[NV];
@@ -96,6 +98,11 @@ __device__ __forceinline__ void warp_key_block(const T* ks, const T* vs, const f
     }
   }
   const int key = first_key + lane;
+  if (softcap > 0.0f) {
+    const float inv_cap = 1.0f / softcap;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) s[v] = softcap * tanhf(s[v] * inv_cap);
+  }
 #pragma unroll
   for (int v = 0; v < NV; ++v) {
     const int p = qpos[v];
@@ -186,7 +193,8 @@ prefill_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
                          T* __restrict__ out, const int* __restrict__ block_table, int table_stride,
                          const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                          const int* __restrict__ prefix_len, const int* __restrict__ rows, int nh, int nkv,
-                         int page_size, int window, float scale, int tile_tokens, int head_chunks, int hd) {
+                         int page_size, int window, float scale, int tile_tokens, int head_chunks, int hd,
+                         int hd_v, float softcap) {
   using G = RowGeom<T>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* qs = reinterpret_cast<float*>(smem_raw);                        // [32][D]
@@ -233,25 +241,25 @@ prefill_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
   for (int kb = k_begin; kb < kv_end; kb += KB) {
     __syncthreads();                                   // the previous block is no longer read
     load_key_block<T>(ks, k_cache, table, page_size, nkv, kvh, kb, kv_end, hd, threadIdx.x, blockDim.x);
-    load_key_block<T>(vs, v_cache, table, page_size, nkv, kvh, kb, kv_end, hd, threadIdx.x, blockDim.x);
+    load_key_block<T>(vs, v_cache, table, page_size, nkv, kvh, kb, kv_end, hd_v, threadIdx.x, blockDim.x);
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
     const bool touches = warp_p_max >= kb && (window <= 0 || kb + KB - 1 > warp_p_min - window);
     if (touches)
-      warp_key_block<T>(ks, vs, qs + warp * NV * D, qpos, kb, kv_end, window, st, ps + warp * KB * NV);
+      warp_key_block<T>(ks, vs, qs + warp * NV * D, qpos, kb, kv_end, window, st, ps + warp * KB * NV, softcap);
   }
 #pragma unroll
   for (int v = 0; v < NV; ++v) {
     const int vec = warp * NV + v;
     if (vec >= nvec) continue;
     const int tok = vec / group, head = head_base + vec % group;
-    T* dst = out + (static_cast<size_t>(q_begin + tok0 + tok) * nh + head) * hd;
+    T* dst = out + (static_cast<size_t>(q_begin + tok0 + tok) * nh + head) * hd_v;
     const float inv = st.l[v] > 0.0f ? 1.0f / st.l[v] : 0.0f;
 #pragma unroll
     for (int k = 0; k < PAIRS; ++k) {
       const int dim = 2 * lane + 64 * k;
-      if (dim < hd) {
+      if (dim < hd_v) {
         dst[dim] = from_f32<T>(st.acc[v][2 * k] * inv);
         dst[dim + 1] = from_f32<T>(st.acc[v][2 * k + 1] * inv);
       }
@@ -272,7 +280,8 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
                         T* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml,
                         const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_q,
                         const int* __restrict__ kv_len, const int* __restrict__ rows, int nh, int nkv,
-                        int page_size, int window, float scale, int vec_groups, int stages, int hd) {
+                        int page_size, int window, float scale, int vec_groups, int stages, int hd, int hd_v,
+                        float softcap) {
   using G = RowGeom<T>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* qs = reinterpret_cast<float*>(smem_raw);                        // [NV][D]
@@ -315,7 +324,7 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
     if (issue < blk_hi) {
       T* t = my_tiles + s * tile_elems;
       load_key_block<T>(t, k_cache, table, page_size, nkv, kvh, k_begin + issue * KB, kv_end, hd, lane, 32);
-      load_key_block<T>(t + KB * G::STRIDE, v_cache, table, page_size, nkv, kvh, k_begin + issue * KB, kv_end, hd, lane, 32);
+      load_key_block<T>(t + KB * G::STRIDE, v_cache, table, page_size, nkv, kvh, k_begin + issue * KB, kv_end, hd_v, lane, 32);
     }
     cp_async_commit();
     issue += DEC_WARPS;
@@ -327,7 +336,7 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
       if (issue < blk_hi) {
         T* t = my_tiles + s_issue * tile_elems;
         load_key_block<T>(t, k_cache, table, page_size, nkv, kvh, k_begin + issue * KB, kv_end, hd, lane, 32);
-        load_key_block<T>(t + KB * G::STRIDE, v_cache, table, page_size, nkv, kvh, k_begin + issue * KB, kv_end, hd, lane, 32);
+        load_key_block<T>(t + KB * G::STRIDE, v_cache, table, page_size, nkv, kvh, k_begin + issue * KB, kv_end, hd_v, lane, 32);
       }
       cp_async_commit();
       issue += DEC_WARPS;
@@ -335,14 +344,14 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
     } else {
       T* t = my_tiles;
       load_key_block<T>(t, k_cache, table, page_size, nkv, kvh, k_begin + blk * KB, kv_end, hd, lane, 32);
-      load_key_block<T>(t + KB * G::STRIDE, v_cache, table, page_size, nkv, kvh, k_begin + blk * KB, kv_end, hd, lane, 32);
+      load_key_block<T>(t + KB * G::STRIDE, v_cache, table, page_size, nkv, kvh, k_begin + blk * KB, kv_end, hd_v, lane, 32);
       cp_async_commit();
       cp_async_wait<0>();
     }
     __syncwarp();
     const T* t = my_tiles + stage * tile_elems;
     warp_key_block<T>(t, t + KB * G::STRIDE, qs, qpos, k_begin + blk * KB, kv_end, window, st,
-                      ps + warp * KB * NV);
+                      ps + warp * KB * NV, softcap);
     stage = (stage + 1) % stages;
   }
   cp_async_wait<0>();
@@ -378,7 +387,7 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
     }
     const int head = head0 + v;
     if (splits == 1) {
-      if (dim < hd) out[(static_cast<size_t>(tok) * nh + head) * hd + dim] = from_f32<T>(l > 0.0f ? o / l : 0.0f);
+      if (dim < hd_v) out[(static_cast<size_t>(tok) * nh + head) * hd_v + dim] = from_f32<T>(l > 0.0f ? o / l : 0.0f);
     } else {
       const size_t slot = (static_cast<size_t>(blockIdx.z) * nh + head) * splits + split;
       part_acc[slot * D + dim] = o;
@@ -415,7 +424,7 @@ template <typename T>
 static int launch_prefill(const void* q, const void* kc, const void* vc, void* out, const int* block_table,
                           int table_stride, const int* cu_q, const int* kv_len, const int* prefix_len,
                           const int* rows, int n_rows, int max_q_len, int nh, int nkv, int page_size, int window,
-                          float scale, int hd, cudaStream_t stream) {
+                          float scale, int hd, int hd_v, float softcap, cudaStream_t stream) {
   using G = RowGeom<T>;
   const int group = nh / nkv;
   const int head_chunks = (group + 31) / 32;                  // more than 32 query heads per KV head: several CTAs
@@ -433,7 +442,7 @@ static int launch_prefill(const void* q, const void* kc, const void* vc, void* o
   prefill_attention_kernel<T><<<grid, PF_WARPS * 32, smem, stream>>>(
       static_cast<const T*>(q), static_cast<const T*>(kc), static_cast<const T*>(vc), static_cast<T*>(out),
       block_table, table_stride, cu_q, kv_len, prefix_len, rows, nh, nkv, page_size, window, scale, tile_tokens,
-      head_chunks, hd);
+      head_chunks, hd, hd_v, softcap);
   return b200_check_launch();
 }
 
@@ -441,7 +450,7 @@ template <typename T>
 static int launch_decode(const void* q, const void* kc, const void* vc, void* out, float* part_acc, float* part_ml,
                          const int* block_table, int table_stride, const int* cu_q, const int* kv_len,
                          const int* rows, int n_rows, int nh, int nkv, int page_size, int window, float scale,
-                         int splits, int hd, cudaStream_t stream) {
+                         int splits, int hd, int hd_v, float softcap, cudaStream_t stream) {
   using G = RowGeom<T>;
   const int group = nh / nkv;
   const int vec_groups = (group + NV - 1) / NV;
@@ -467,12 +476,12 @@ static int launch_decode(const void* q, const void* kc, const void* vc, void* ou
   decode_attention_kernel<T, DEC_WARPS><<<grid, DEC_WARPS * 32, smem, stream>>>(
       static_cast<const T*>(q), static_cast<const T*>(kc), static_cast<const T*>(vc), static_cast<T*>(out),
       part_acc, part_ml, block_table, table_stride, cu_q, kv_len, rows, nh, nkv, page_size, window, scale,
-      vec_groups, stages, hd);
+      vec_groups, stages, hd, hd_v, softcap);
   int rc = b200_check_launch();
   if (rc != 0 || splits == 1) return rc;
   dim3 mgrid(n_rows, nh);
   decode_merge_kernel<T><<<mgrid, D >= 128 ? 128 : 64, 0, stream>>>(static_cast<T*>(out), part_acc, part_ml, cu_q,
-                                                                   rows, nh, splits, hd);
+                                                                   rows, nh, splits, hd_v);
   return b200_check_launch();
 }
 
@@ -483,17 +492,19 @@ B200_EXPORT int b200_prefill_attention(const void* q, const void* k_cache, const
                                        const int* block_table, int table_stride, const int* cu_q,
                                        const int* kv_len, const int* prefix_len, const int* rows, int n_rows,
                                        int max_q_len, int nh, int nkv, int page_size, int window, float scale,
-                                       int dtype, int head_dim, cudaStream_t stream) {
+                                       int dtype, int head_dim, int v_head_dim, float softcap, cudaStream_t stream) {
   if (n_rows <= 0 || max_q_len <= 0) return 0;
   if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0) return B200_BAD_SIZE;
   if (head_dim <= 0 || head_dim > D || (head_dim & 1)) return B200_BAD_SIZE;
+  if (v_head_dim <= 0 || v_head_dim > D || (v_head_dim & 1)) return B200_BAD_SIZE;
   if (dtype == B200_F32)
     return launch_prefill<float>(q, k_cache, v_cache, out, block_table, table_stride, cu_q, kv_len, prefix_len,
-                                 rows, n_rows, max_q_len, nh, nkv, page_size, window, scale, head_dim, stream);
+                                 rows, n_rows, max_q_len, nh, nkv, page_size, window, scale, head_dim, v_head_dim,
+                                 softcap, stream);
   if (dtype == B200_BF16)
     return launch_prefill<__nv_bfloat16>(q, k_cache, v_cache, out, block_table, table_stride, cu_q, kv_len,
                                          prefix_len, rows, n_rows, max_q_len, nh, nkv, page_size, window, scale,
-                                         head_dim, stream);
+                                         head_dim, v_head_dim, softcap, stream);
   return B200_BAD_DTYPE;
 }
 
@@ -508,18 +519,20 @@ B200_EXPORT int b200_decode_attention(const void* q, const void* k_cache, const 
                                       float* scratch, const int* block_table, int table_stride,
                                       const int* cu_q, const int* kv_len, const int* rows, int n_rows, int nh,
                                       int nkv, int page_size, int window, float scale, int splits, int dtype,
-                                      int head_dim, cudaStream_t stream) {
+                                      int head_dim, int v_head_dim, float softcap, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || splits <= 0) return B200_BAD_SIZE;
   if (head_dim <= 0 || head_dim > D || (head_dim & 1)) return B200_BAD_SIZE;
+  if (v_head_dim <= 0 || v_head_dim > D || (v_head_dim & 1)) return B200_BAD_SIZE;
   float* part_acc = scratch;
   float* part_ml = scratch + static_cast<size_t>(n_rows) * nh * splits * D;
   if (dtype == B200_F32)
     return launch_decode<float>(q, k_cache, v_cache, out, part_acc, part_ml, block_table, table_stride, cu_q,
-                                kv_len, rows, n_rows, nh, nkv, page_size, window, scale, splits, head_dim, stream);
+                                kv_len, rows, n_rows, nh, nkv, page_size, window, scale, splits, head_dim, v_head_dim,
+                                softcap, stream);
   if (dtype == B200_BF16)
     return launch_decode<__nv_bfloat16>(q, k_cache, v_cache, out, part_acc, part_ml, block_table, table_stride,
                                         cu_q, kv_len, rows, n_rows, nh, nkv, page_size, window, scale, splits,
-                                        head_dim, stream);
+                                        head_dim, v_head_dim, softcap, stream);
   return B200_BAD_DTYPE;
 }

@@ -1,0 +1,118 @@
+// Element-wise ends of gated mixers and of the PolyNorm feed-forward, all sums in float.
+//
+//   poly_norm            out = a N(z) + b N(z^2) + c N(z^3) + e,  N(y) = y / sqrt(mean(y^2) + eps) over a token's
+//                        vector, powers taken element by element; (a, b, c, e) are four floats on the device
+//   head_unit_norm_gate  out[t][h][:] = o[t][h][:] / sqrt(mean(o[t][h][:]^2) + eps) * silu(g[t][h][:])
+//   sigmoid_gate_mul     out[t][c] = a[t][c] * sigmoid(g[t][c])
+//
+// `g` is a column range of a wider matrix (row stride g_stride), so a gate that was projected together with
+// other things is read where it lies.
+#include "common.cuh"
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+poly_norm_kernel(T* __restrict__ out, const T* __restrict__ z, const float* __restrict__ coef, float eps, int width) {
+  __shared__ float scratch[33];
+  const size_t base = static_cast<size_t>(blockIdx.x) * width;
+  float s2 = 0.0f, s4 = 0.0f, s6 = 0.0f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = to_f32<T>(z[base + c]);
+    const float v2 = v * v, v3 = v2 * v;
+    s2 += v2;
+    s4 = fmaf(v2, v2, s4);
+    s6 = fmaf(v3, v3, s6);
+  }
+  s2 = block_sum(s2, scratch);
+  s4 = block_sum(s4, scratch);
+  s6 = block_sum(s6, scratch);
+  const float n = static_cast<float>(width);
+  const float r1 = coef[0] / sqrtf(s2 / n + eps), r2 = coef[1] / sqrtf(s4 / n + eps), r3 = coef[2] / sqrtf(s6 / n + eps);
+  const float e = coef[3];
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = to_f32<T>(z[base + c]);
+    const float v2 = v * v;
+    out[base + c] = from_f32<T>(fmaf(r1, v, fmaf(r2, v2, fmaf(r3, v2 * v, e))));
+  }
+}
+
+// one warp per (token, head)
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_unit_norm_gate_kernel(T* __restrict__ out, const float* __restrict__ o, const T* __restrict__ g, int g_stride,
+                           int heads, int dv, float eps, long long vectors) {
+  const long long vec = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+  if (vec >= vectors) return;
+  const int lane = threadIdx.x & 31;
+  const long long t = vec / heads;
+  const int h = static_cast<int>(vec - t * heads);
+  const float* src = o + (t * heads + h) * dv;
+  float ss = 0.0f;
+  for (int j = lane; j < dv; j += 32) ss = fmaf(src[j], src[j], ss);
+  ss = warp_sum(ss);
+  const float r = 1.0f / sqrtf(ss / static_cast<float>(dv) + eps);
+  const T* gate = g + t * g_stride + static_cast<size_t>(h) * dv;
+  T* dst = out + (t * heads + h) * dv;
+  for (int j = lane; j < dv; j += 32) {
+    const float x = to_f32<T>(gate[j]);
+    dst[j] = from_f32<T>(src[j] * r * (x / (1.0f + expf(-x))));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+sigmoid_gate_mul_kernel(T* out, const T* a, const T* __restrict__ g, int g_stride, int width) {   // out may be a
+  const size_t t = blockIdx.x;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float x = to_f32<T>(g[t * g_stride + c]);
+    out[t * width + c] = from_f32<T>(to_f32<T>(a[t * width + c]) / (1.0f + expf(-x)));
+  }
+}
+
+B200_EXPORT int b200_poly_norm(void* out, const void* z, const float* coef, float eps, int tokens, int width,
+                               int dtype, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (width <= 0) return B200_BAD_SIZE;
+  if (dtype == B200_F32)
+    poly_norm_kernel<float><<<tokens, 256, 0, stream>>>(static_cast<float*>(out), static_cast<const float*>(z), coef,
+                                                        eps, width);
+  else if (dtype == B200_BF16)
+    poly_norm_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(out),
+                                                                static_cast<const __nv_bfloat16*>(z), coef, eps, width);
+  else
+    return B200_BAD_DTYPE;
+  return b200_check_launch();
+}
+
+B200_EXPORT int b200_head_unit_norm_gate(void* out, const float* o, const void* g, int g_stride, int tokens, int heads,
+                                         int dv, float eps, int dtype, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (heads <= 0 || dv <= 0) return B200_BAD_SIZE;
+  const long long vectors = static_cast<long long>(tokens) * heads;
+  const unsigned blocks = static_cast<unsigned>((vectors + 3) / 4);
+  if (dtype == B200_F32)
+    head_unit_norm_gate_kernel<float><<<blocks, 128, 0, stream>>>(static_cast<float*>(out), o,
+                                                                   static_cast<const float*>(g), g_stride, heads, dv, eps,
+                                                                   vectors);
+  else if (dtype == B200_BF16)
+    head_unit_norm_gate_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(
+        static_cast<__nv_bfloat16*>(out), o, static_cast<const __nv_bfloat16*>(g), g_stride, heads, dv, eps, vectors);
+  else
+    return B200_BAD_DTYPE;
+  return b200_check_launch();
+}
+
+B200_EXPORT int b200_sigmoid_gate_mul(void* out, const void* a, const void* g, int g_stride, int tokens, int width,
+                                      int dtype, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (width <= 0) return B200_BAD_SIZE;
+  if (dtype == B200_F32)
+    sigmoid_gate_mul_kernel<float><<<tokens, 256, 0, stream>>>(static_cast<float*>(out), static_cast<const float*>(a),
+                                                               static_cast<const float*>(g), g_stride, width);
+  else if (dtype == B200_BF16)
+    sigmoid_gate_mul_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>(
+        static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(g),
+        g_stride, width);
+  else
+    return B200_BAD_DTYPE;
+  return b200_check_launch();
+}

@@ -1,0 +1,193 @@
+// A float32 residual stream with one-gain RMS norms, and short causal convolutions over time whose last
+// inputs are per-request state.
+//
+//   residual_scale   x[t] += y[t] (optional, the sum in float), s[t] = gain / sqrt(mean(x[t]^2) + eps)
+//   scaled_rows      out[r] = x[rows[r]] * s[rows[r]]                       (the norm itself, for chosen rows)
+//   causal_taps      y[t][c] = (identity ? u[t][c] : 0) + sum_j w[c][j] * u[t - taps + 1 + j][c],
+//                    u[t][c] = in[t][c] * (s ? s[t] : 1)
+//   taps_state_update   the last taps - 1 inputs u of every row become the row's state
+//
+// Inputs before a row's first token of this step come from the request's state slot,
+// state[slot][taps - 1][C] in float32, oldest first; a row that starts at position 0 reads zeros, and positions
+// before the sequence's start are stored as zeros, so the state of a sequence shorter than taps - 1 is right
+// too.  The state is read by causal_taps and written by taps_state_update, a kernel of its own behind it in the
+// stream: in one kernel the block of a row's last token could overwrite what the block of its first token has
+// yet to read.  Slot 0 belongs to padding rows and may hold anything.
+//
+// A row's result depends on its own tokens only; sums over a token's vector are taken in a fixed order.
+#include "token_conv.cuh"
+
+// ------------------------------------------------------------------ residual sum and the norm's scale
+template <typename TY>
+__global__ void __launch_bounds__(256)
+residual_scale_kernel(float* __restrict__ x, const TY* __restrict__ y, const float* __restrict__ gain, float eps,
+                      float* __restrict__ scale, int width) {
+  __shared__ float scratch[33];
+  const size_t base = static_cast<size_t>(blockIdx.x) * width;
+  float ss = 0.0f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float v = x[base + c];
+    if (y != nullptr) {
+      v += to_f32<TY>(y[base + c]);
+      x[base + c] = v;
+    }
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  if (threadIdx.x == 0 && scale != nullptr) scale[blockIdx.x] = gain[0] / sqrtf(ss / static_cast<float>(width) + eps);
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(256)
+scaled_rows_kernel(TO* __restrict__ out, const float* __restrict__ x, const float* __restrict__ scale,
+                   const int* __restrict__ rows, int width) {
+  const int t = rows ? rows[blockIdx.x] : blockIdx.x;
+  const float s = scale[t];
+  for (int c = threadIdx.x; c < width; c += blockDim.x)
+    out[static_cast<size_t>(blockIdx.x) * width + c] = from_f32<TO>(x[static_cast<size_t>(t) * width + c] * s);
+}
+
+// ------------------------------------------------------------------ the convolution
+// grid (tokens, channel tiles of 256)
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+causal_taps_kernel(TapsInput<TI> in, TO* __restrict__ out, int out_stride, int identity) {
+  const int t = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= in.channels) return;
+  const TapsRow row = taps_row(in, t);
+  const float y = taps_value(in, row, t, c, identity != 0);
+  out[static_cast<size_t>(t) * out_stride + c] = from_f32<TO>(y);
+}
+
+// grid (rows, channel tiles of 256): new state k holds the input at position end - (taps - 1) + k
+template <typename TI>
+__global__ void __launch_bounds__(256)
+taps_state_update_kernel(TapsInput<TI> in, int num_rows) {
+  const int r = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= in.channels || r >= num_rows) return;
+  const int hist = in.taps - 1;
+  const int first = in.cu_q[r], n = in.cu_q[r + 1] - first;
+  const int prefix = in.prefix_len[r];
+  const int slot = in.state_slots[r];
+  float* st = in.state + static_cast<size_t>(slot) * hist * in.channels;
+  float fresh[TAPS_MAX - 1];
+#pragma unroll
+  for (int k = 0; k < TAPS_MAX - 1; ++k) {
+    if (k >= hist) break;
+    const int pos = prefix + n - hist + k;            // absolute position that lands in state k
+    float v = 0.0f;
+    if (pos >= prefix) {
+      const int t = first + (pos - prefix);
+      v = to_f32<TI>(in.x[static_cast<size_t>(t) * in.in_stride + c]) * (in.scale ? in.scale[t] : 1.0f);
+    } else if (pos >= 0 && prefix > 0) {
+      v = st[static_cast<size_t>(pos - prefix + hist) * in.channels + c];
+    }
+    fresh[k] = v;
+  }
+#pragma unroll
+  for (int k = 0; k < TAPS_MAX - 1; ++k) {
+    if (k >= hist) break;
+    st[static_cast<size_t>(k) * in.channels + c] = fresh[k];
+  }
+}
+
+// ------------------------------------------------------------------ C interface
+B200_EXPORT int b200_residual_scale(float* x, const void* y, int y_dtype, const float* gain, float eps, float* scale,
+                                    int tokens, int width, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (width <= 0) return B200_BAD_SIZE;
+  if (y == nullptr || y_dtype == B200_F32)
+    residual_scale_kernel<float><<<tokens, 256, 0, stream>>>(x, static_cast<const float*>(y), gain, eps, scale, width);
+  else if (y_dtype == B200_BF16)
+    residual_scale_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>(x, static_cast<const __nv_bfloat16*>(y), gain,
+                                                                      eps, scale, width);
+  else
+    return B200_BAD_DTYPE;
+  return b200_check_launch();
+}
+
+B200_EXPORT int b200_scaled_rows(void* out, int out_dtype, const float* x, const float* scale, const int* rows,
+                                 int n, int width, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (width <= 0) return B200_BAD_SIZE;
+  if (out_dtype == B200_F32)
+    scaled_rows_kernel<float><<<n, 256, 0, stream>>>(static_cast<float*>(out), x, scale, rows, width);
+  else if (out_dtype == B200_BF16)
+    scaled_rows_kernel<__nv_bfloat16><<<n, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(out), x, scale, rows, width);
+  else
+    return B200_BAD_DTYPE;
+  return b200_check_launch();
+}
+
+template <typename TI>
+static int launch_taps(const TapsInput<TI>& in, void* out, int out_dtype, int out_stride, int identity, int tokens,
+                       int num_rows, int update_state, cudaStream_t stream) {
+  const dim3 grid(tokens, (in.channels + 255) / 256);
+  if (out_dtype == B200_F32)
+    causal_taps_kernel<TI, float><<<grid, 256, 0, stream>>>(in, static_cast<float*>(out), out_stride, identity);
+  else if (out_dtype == B200_BF16)
+    causal_taps_kernel<TI, __nv_bfloat16><<<grid, 256, 0, stream>>>(in, static_cast<__nv_bfloat16*>(out), out_stride,
+                                                                    identity);
+  else
+    return B200_BAD_DTYPE;
+  int rc = b200_check_launch();
+  if (rc != 0 || !update_state || in.taps <= 1) return rc;
+  const dim3 sgrid(num_rows, (in.channels + 255) / 256);
+  taps_state_update_kernel<TI><<<sgrid, 256, 0, stream>>>(in, num_rows);
+  return b200_check_launch();
+}
+
+template <typename TI>
+static TapsInput<TI> taps_input(const void* x, int in_stride, const float* scale, const float* w, int taps,
+                                int channels, float* state, const int* row_of_token, const int* cu_q,
+                                const int* prefix_len, const int* state_slots) {
+  TapsInput<TI> in;
+  in.x = static_cast<const TI*>(x); in.in_stride = in_stride; in.scale = scale; in.w = w; in.taps = taps;
+  in.channels = channels; in.state = state; in.row_of_token = row_of_token; in.cu_q = cu_q;
+  in.prefix_len = prefix_len; in.state_slots = state_slots;
+  return in;
+}
+
+// out[t][c] for c < channels; `x` rows are in_stride wide, `out` rows out_stride.  With update_state the rows'
+// states are brought up to date behind the convolution (a second kernel).
+B200_EXPORT int b200_causal_taps(const void* x, int in_dtype, int in_stride, const float* scale, const float* w,
+                                 int taps, int channels, float* state, const int* row_of_token, const int* cu_q,
+                                 const int* prefix_len, const int* state_slots, void* out, int out_dtype,
+                                 int out_stride, int identity, int tokens, int num_rows, int update_state,
+                                 cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (channels <= 0 || taps < 1 || taps > TAPS_MAX || num_rows <= 0) return B200_BAD_SIZE;
+  if ((channels + 255) / 256 > 65535) return B200_BAD_SIZE;
+  if (in_dtype == B200_F32)
+    return launch_taps<float>(taps_input<float>(x, in_stride, scale, w, taps, channels, state, row_of_token, cu_q,
+                                                prefix_len, state_slots),
+                              out, out_dtype, out_stride, identity, tokens, num_rows, update_state, stream);
+  if (in_dtype == B200_BF16)
+    return launch_taps<__nv_bfloat16>(taps_input<__nv_bfloat16>(x, in_stride, scale, w, taps, channels, state,
+                                                                row_of_token, cu_q, prefix_len, state_slots),
+                                      out, out_dtype, out_stride, identity, tokens, num_rows, update_state, stream);
+  return B200_BAD_DTYPE;
+}
+
+// Only the state update (for a caller whose own kernel did the convolution).
+B200_EXPORT int b200_taps_state_update(const void* x, int in_dtype, int in_stride, const float* scale, int taps,
+                                       int channels, float* state, const int* cu_q, const int* prefix_len,
+                                       const int* state_slots, int num_rows, cudaStream_t stream) {
+  if (num_rows <= 0 || taps <= 1) return 0;
+  if (channels <= 0 || taps > TAPS_MAX || (channels + 255) / 256 > 65535) return B200_BAD_SIZE;
+  const dim3 sgrid(num_rows, (channels + 255) / 256);
+  if (in_dtype == B200_F32)
+    taps_state_update_kernel<float><<<sgrid, 256, 0, stream>>>(
+        taps_input<float>(x, in_stride, scale, nullptr, taps, channels, state, nullptr, cu_q, prefix_len, state_slots),
+        num_rows);
+  else if (in_dtype == B200_BF16)
+    taps_state_update_kernel<__nv_bfloat16><<<sgrid, 256, 0, stream>>>(
+        taps_input<__nv_bfloat16>(x, in_stride, scale, nullptr, taps, channels, state, nullptr, cu_q, prefix_len,
+                                  state_slots),
+        num_rows);
+  else
+    return B200_BAD_DTYPE;
+  return b200_check_launch();
+}

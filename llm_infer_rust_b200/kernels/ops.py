@@ -290,8 +290,11 @@ def tcgen05_attention_launches() -> tuple:
 
 def prefill_attention(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefix_len, rows, n_rows,
                       max_q_len, num_heads, num_kv_heads, head_dim, page_size, window, scale,
-                      tiles_per_cta: int = 0) -> None:
+                      tiles_per_cta: int = 0, v_head_dim: Optional[int] = None, softcap: float = 0.0) -> None:
     """Causal attention of prompt portions over the paged cache (rows: which batch rows).
+
+    ``v_head_dim``: the width of a value (and of an output) vector where it differs from a key's;
+    ``softcap`` > 0: a score becomes cap * tanh(score / cap) before the mask.  Both take the all-sizes kernel.
 
     ``tiles_per_cta`` (head size 128 on the tcgen05 kernel only): 1 or 2 tiles of 128 query vectors per
     CTA, 0 lets the kernel's launcher choose by the size of the grid."""
@@ -301,7 +304,9 @@ def prefill_attention(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefi
         return
     if k_cache.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelError("q, cache and output must share a dtype")
-    if decode_uses_tensor_cores(q.dtype, num_heads, num_kv_heads, head_dim, page_size):
+    dv = int(v_head_dim or head_dim)
+    plain = dv == head_dim and not softcap > 0.0
+    if plain and decode_uses_tensor_cores(q.dtype, num_heads, num_kv_heads, head_dim, page_size):
         if k_cache.shape[1] != num_kv_heads or k_cache.shape[2] != page_size:
             raise KernelError("the cache must be [pages + 1, kv_heads, page_size, head_dim]")
         box_rows = min(page_size, 32)
@@ -321,10 +326,10 @@ def prefill_attention(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefi
             num_kv_heads, page_size, int(window or 0), ctypes.c_float(scale), _p(error_word(q.device)), _stream())
         _ok(rc, "prefill_attention_mma")
         return
-    rc = _attention(head_dim).b200_prefill_attention(
+    rc = _attention(max(head_dim, dv)).b200_prefill_attention(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(block_table), block_table.shape[-1], _p(cu_q),
         _p(kv_len), _p(prefix_len), _p(rows), n_rows, max_q_len, num_heads, num_kv_heads, page_size,
-        int(window or 0), ctypes.c_float(scale), _code(q), head_dim, _stream())
+        int(window or 0), ctypes.c_float(scale), _code(q), head_dim, dv, ctypes.c_float(softcap or 0.0), _stream())
     _ok(rc, "prefill_attention")
 
 
@@ -367,9 +372,10 @@ def kv_tensor_map(cache: torch.Tensor, box_rows: int):
 
 
 def decode_ctas_per_split(dtype: torch.dtype, n_rows: int, num_heads: int, num_kv_heads: int, head_dim: int,
-                          page_size: int) -> int:
-    """CTAs that the decode kernel launches for each split of the keys."""
-    if decode_uses_tensor_cores(dtype, num_heads, num_kv_heads, head_dim, page_size):
+                          page_size: int, plain: bool = True) -> int:
+    """CTAs that the decode kernel launches for each split of the keys (``plain``: values as wide as keys and
+    no soft-cap, the case the tensor-core kernel takes)."""
+    if plain and decode_uses_tensor_cores(dtype, num_heads, num_kv_heads, head_dim, page_size):
         return n_rows * num_kv_heads
     return n_rows * num_kv_heads * ((num_heads // num_kv_heads + 3) // 4)
 
@@ -380,18 +386,22 @@ def decode_scratch_floats(n_rows: int, num_heads: int, head_dim: int, splits: in
 
 
 def decode_attention(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_len, rows, n_rows,
-                     num_heads, num_kv_heads, head_dim, page_size, window, scale, splits) -> None:
-    """Attention of single decoded tokens, the keys split over ``splits`` blocks per row."""
+                     num_heads, num_kv_heads, head_dim, page_size, window, scale, splits,
+                     v_head_dim: Optional[int] = None, softcap: float = 0.0) -> None:
+    """Attention of single decoded tokens, the keys split over ``splits`` blocks per row (``v_head_dim``,
+    ``softcap``: see ``prefill_attention``)."""
     _cuda(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_len, rows)
     _contig(q, k_cache, v_cache, out, block_table, scratch)
     if n_rows == 0:
         return
     if k_cache.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelError("q, cache and output must share a dtype")
-    need = decode_scratch_floats(n_rows, num_heads, head_dim, splits)
+    dv = int(v_head_dim or head_dim)
+    plain = dv == head_dim and not softcap > 0.0
+    need = decode_scratch_floats(n_rows, num_heads, max(head_dim, dv), splits)
     if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
         raise KernelError(f"decode attention needs {need} floats of scratch")
-    if decode_uses_tensor_cores(q.dtype, num_heads, num_kv_heads, head_dim, page_size):
+    if plain and decode_uses_tensor_cores(q.dtype, num_heads, num_kv_heads, head_dim, page_size):
         if k_cache.shape[1] != num_kv_heads or k_cache.shape[2] != page_size:
             raise KernelError("the cache must be [pages + 1, kv_heads, page_size, head_dim]")
         box_rows = min(page_size, 32)
@@ -402,10 +412,10 @@ def decode_attention(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_le
         in_kernel = splits == 1 or (splits in (2, 4, 8) and splits * num_kv_heads * n_rows <= _sm_count(q.device))
         _ok(rc, "decode_attention_mma", 1 if in_kernel else 2)      # (a cluster of 2, 4 or 8 splits combines them itself)
         return
-    rc = _attention(head_dim).b200_decode_attention(
+    rc = _attention(max(head_dim, dv)).b200_decode_attention(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(scratch), _p(block_table), block_table.shape[-1],
         _p(cu_q), _p(kv_len), _p(rows), n_rows, num_heads, num_kv_heads, page_size, int(window or 0),
-        ctypes.c_float(scale), splits, _code(q), head_dim, _stream())
+        ctypes.c_float(scale), splits, _code(q), head_dim, dv, ctypes.c_float(softcap or 0.0), _stream())
     _ok(rc, "decode_attention", 2 if splits > 1 else 1)
 
 
@@ -1213,3 +1223,193 @@ def sample(logits: torch.Tensor, params: torch.Tensor, uniforms: Optional[torch.
                                                       _p(uniforms), _p(error_word(logits.device)), _stream())
     _ok(rc, "sample")
     return out
+
+
+# --------------------------------------------------------------------------- float32 residual stream, one-gain norms
+def _token_conv():
+    return load_cuda_library("token_conv.cu")
+
+
+def _f32(*tensors: Optional[torch.Tensor]) -> None:
+    for t in tensors:
+        if t is not None and t.dtype != torch.float32:
+            raise KernelError("this operand must be float32")
+
+
+def _i32(*tensors: Optional[torch.Tensor]) -> None:
+    for t in tensors:
+        if t is not None and t.dtype != torch.int32:
+            raise KernelError("index arrays must be int32")
+
+
+def residual_scale(x: torch.Tensor, y: Optional[torch.Tensor], gain: torch.Tensor, eps: float,
+                   want_scale: bool = True) -> Optional[torch.Tensor]:
+    """x += y in place (x float32 [tokens, width], the sum in float; ``y`` None: nothing is added), and the scale
+    of a one-gain RMS norm of the new x for every token: gain / sqrt(mean(x^2) + eps), float32 [tokens]."""
+    _cuda(x, y, gain)
+    _contig(x, y, gain)
+    _f32(x, gain)
+    if x.dim() != 2 or (y is not None and y.shape != x.shape) or gain.numel() != 1:
+        raise KernelError("residual_scale takes x and y [tokens, width] and one gain")
+    scale = torch.empty(x.shape[0], dtype=torch.float32, device=x.device) if want_scale else None
+    rc = _token_conv().b200_residual_scale(_p(x), _p(y), _code(y) if y is not None else F32, _p(gain),
+                                           ctypes.c_float(eps), _p(scale), x.shape[0], x.shape[1], _stream())
+    _ok(rc, "residual_scale")
+    return scale
+
+
+def scaled_rows(x: torch.Tensor, scale: torch.Tensor, rows: Optional[torch.Tensor], out_dtype: torch.dtype) -> torch.Tensor:
+    """out[r] = x[rows[r]] * scale[rows[r]] (rows None: every row), rounded once to ``out_dtype``."""
+    _cuda(x, scale, rows)
+    _contig(x, scale, rows)
+    _f32(x, scale)
+    _i32(rows)
+    n = x.shape[0] if rows is None else rows.numel()
+    out = torch.empty((n, x.shape[1]), dtype=out_dtype, device=x.device)
+    rc = _token_conv().b200_scaled_rows(_p(out), _code(out), _p(x), _p(scale), _p(rows), n, x.shape[1], _stream())
+    _ok(rc, "scaled_rows")
+    return out
+
+
+def causal_taps(x: torch.Tensor, weight: Optional[torch.Tensor], state: Optional[torch.Tensor], ctx,
+                out_dtype: torch.dtype, scale: Optional[torch.Tensor] = None, identity: bool = False,
+                channels: Optional[int] = None, update_state: bool = True) -> torch.Tensor:
+    """A short causal convolution over time on every channel, for a step's rows:
+
+        y[t] = (u[t] if identity) + sum_j weight[:, j] * u[t - taps + 1 + j],   u[t] = x[t] * scale[t]
+
+    with the inputs before a row's first token taken from ``state[slot]`` ([taps - 1, channels] float32, oldest
+    first; zeros for a row that starts its sequence), and the rows' states brought up to date afterwards.
+    ``channels``: only the first so many columns of ``x`` pass through.  ``ctx`` gives the step's index arrays."""
+    _cuda(x, weight, state, scale)
+    _contig(x, weight, state, scale)
+    _f32(weight, state, scale)
+    c = int(channels or x.shape[1])
+    taps = 1 if weight is None else weight.shape[1]
+    if weight is not None and weight.shape[0] != c:
+        raise KernelError("the taps must be [channels, taps]")
+    if taps > 1 and (state is None or tuple(state.shape[1:]) != (taps - 1, c)):
+        raise KernelError("the state of a convolution must be [slots + 1, taps - 1, channels]")
+    out = torch.empty((x.shape[0], c), dtype=out_dtype, device=x.device)
+    rc = _token_conv().b200_causal_taps(
+        _p(x), _code(x), x.shape[1], _p(scale), _p(weight), taps, c, _p(state), _p(ctx.row_of_token), _p(ctx.cu_q),
+        _p(ctx.prefix_len), _p(ctx.state_slots), _p(out), _code(out), c, int(bool(identity)), x.shape[0],
+        ctx.num_rows, int(bool(update_state)), _stream())
+    _ok(rc, "causal_taps", 2 if update_state and taps > 1 else 1)
+    return out
+
+
+def taps_state_update(x: torch.Tensor, taps: int, channels: int, state: torch.Tensor, ctx) -> None:
+    """The last ``taps - 1`` rows of x (first ``channels`` columns) of every row of the step become its state."""
+    if taps <= 1:
+        return
+    _cuda(x, state)
+    _contig(x, state)
+    _f32(state)
+    rc = _token_conv().b200_taps_state_update(_p(x), _code(x), x.shape[1], None, taps, channels, _p(state),
+                                              _p(ctx.cu_q), _p(ctx.prefix_len), _p(ctx.state_slots), ctx.num_rows,
+                                              _stream())
+    _ok(rc, "taps_state_update")
+
+
+def conv_qkv_post(x: torch.Tensor, conv_weight: Optional[torch.Tensor], state: Optional[torch.Tensor], ctx,
+                  q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                  inv_freq: Optional[torch.Tensor], rot_dim: int, slots: Optional[torch.Tensor], num_heads: int,
+                  num_kv_heads: int, head_dim: int, v_head_dim: int, vmix: Optional[torch.Tensor] = None,
+                  v_first: Optional[torch.Tensor] = None, v_mode: int = 0) -> None:
+    """Short convolution of the packed q, k, v columns of ``x`` (state as in ``causal_taps``), rotation of q and
+    k by position * inv_freq, value mixing (``v_mode`` 1: this v is written to ``v_first``; 2: v becomes
+    (1 - vmix) v + vmix v_first), q to ``q_out``, k and v into the paged cache at ``slots``."""
+    _cuda(x, conv_weight, state, q_out, k_cache, v_cache, inv_freq, slots, vmix, v_first)
+    _contig(x, conv_weight, state, q_out, k_cache, v_cache, inv_freq, slots, vmix, v_first)
+    _f32(conv_weight, state, inv_freq, vmix, v_first)
+    c = (num_heads + num_kv_heads) * head_dim + num_kv_heads * v_head_dim
+    if x.shape[1] < c or q_out.dtype != x.dtype or k_cache.dtype != x.dtype or v_cache.dtype != x.dtype:
+        raise KernelError("conv_qkv_post: the projection is too narrow, or q, cache and projection differ in dtype")
+    taps = 1 if conv_weight is None else conv_weight.shape[1]
+    if conv_weight is not None and conv_weight.shape[0] != c:
+        raise KernelError("the taps must be [q + k + v channels, taps]")
+    if taps > 1 and (state is None or tuple(state.shape[1:]) != (taps - 1, c)):
+        raise KernelError("the state of a convolution must be [slots + 1, taps - 1, channels]")
+    if tuple(k_cache.shape[1:]) != (num_kv_heads, k_cache.shape[2], head_dim) or \
+            tuple(v_cache.shape[1:]) != (num_kv_heads, k_cache.shape[2], v_head_dim):
+        raise KernelError("the cache must be [pages + 1, kv_heads, page_size, width]")
+    if inv_freq is not None and inv_freq.numel() * 2 != rot_dim:
+        raise KernelError("one frequency for every rotated pair is needed")
+    page_size = k_cache.shape[2]
+    rc = load_cuda_library("conv_qkv_post.cu").b200_conv_qkv_post(
+        _p(x), _code(x), x.shape[1], _p(conv_weight), taps, _p(state), _p(ctx.row_of_token), _p(ctx.cu_q),
+        _p(ctx.prefix_len), _p(ctx.state_slots), _p(q_out), _p(k_cache), _p(v_cache), _p(inv_freq),
+        int(rot_dim if inv_freq is not None else 0), _p(ctx.positions), _p(slots), num_heads, num_kv_heads, head_dim,
+        v_head_dim, page_size, ctypes.c_longlong(k_cache.shape[0] * page_size), _p(vmix), _p(v_first), int(v_mode),
+        x.shape[0], _p(error_word(x.device)), _stream())
+    _ok(rc, "conv_qkv_post")
+
+
+def retention(x: torch.Tensor, state: torch.Tensor, decay: torch.Tensor, inv_freq: Optional[torch.Tensor],
+              rot_dim: int, k_scale: float, ctx, heads: int, head_dim: int, v_head_dim: int) -> torch.Tensor:
+    """o [tokens, heads * v_head_dim] (float32) of S_t = decay S_(t-1) + k_t v_t^T, o_t = S_t^T q_t over the step's
+    rows; q, k (rotated by position * inv_freq, k then times ``k_scale``) and v are the first columns of ``x``;
+    ``state`` [slots + 1, heads, head_dim, v_head_dim] float32 is read (rows with a prefix) and written."""
+    _cuda(x, state, decay, inv_freq)
+    _contig(x, state, decay, inv_freq)
+    _f32(state, decay, inv_freq)
+    if x.shape[1] < heads * (2 * head_dim + v_head_dim) or tuple(state.shape[1:]) != (heads, head_dim, v_head_dim) \
+            or decay.numel() != heads:
+        raise KernelError("retention: sizes of the projection, the state or the decays do not fit")
+    o = torch.empty((x.shape[0], heads * v_head_dim), dtype=torch.float32, device=x.device)
+    rc = load_cuda_library("retention.cu").b200_retention(
+        _p(x), _code(x), x.shape[1], _p(o), _p(state), _p(decay), _p(inv_freq),
+        int(rot_dim if inv_freq is not None else 0), ctypes.c_float(k_scale), _p(ctx.positions), _p(ctx.cu_q),
+        _p(ctx.prefix_len), _p(ctx.state_slots), ctx.num_rows, heads, head_dim, v_head_dim, _stream())
+    _ok(rc, "retention")
+    return o
+
+
+# --------------------------------------------------------------------------- gates and PolyNorm
+def _gated():
+    return load_cuda_library("gated.cu")
+
+
+def poly_norm(z: torch.Tensor, coef: torch.Tensor, eps: float) -> torch.Tensor:
+    """coef[0] N(z) + coef[1] N(z^2) + coef[2] N(z^3) + coef[3], N = division by the root mean square of a row."""
+    _cuda(z, coef)
+    _contig(z, coef)
+    _f32(coef)
+    if coef.numel() != 4 or z.dim() != 2:
+        raise KernelError("poly_norm takes rows and four coefficients")
+    out = torch.empty_like(z)
+    rc = _gated().b200_poly_norm(_p(out), _p(z), _p(coef), ctypes.c_float(eps), z.shape[0], z.shape[1], _code(z),
+                                 _stream())
+    _ok(rc, "poly_norm")
+    return out
+
+
+def head_unit_norm_gate(o: torch.Tensor, packed: torch.Tensor, gate_column: int, heads: int, v_head_dim: int,
+                        eps: float) -> torch.Tensor:
+    """Every head's vector of ``o`` (float32) divided by its root mean square, times silu of the gate that lies
+    in ``packed`` from column ``gate_column`` on; the result has ``packed``'s dtype."""
+    _cuda(o, packed)
+    _contig(o, packed)
+    _f32(o)
+    if packed.shape[1] < gate_column + heads * v_head_dim or o.shape[1] != heads * v_head_dim:
+        raise KernelError("head_unit_norm_gate: the gate's columns do not fit")
+    out = torch.empty((o.shape[0], o.shape[1]), dtype=packed.dtype, device=o.device)
+    gate = packed.view(-1)[gate_column:]
+    rc = _gated().b200_head_unit_norm_gate(_p(out), _p(o), ctypes.c_void_p(gate.data_ptr()), packed.shape[1],
+                                           o.shape[0], heads, v_head_dim, ctypes.c_float(eps), _code(packed), _stream())
+    _ok(rc, "head_unit_norm_gate")
+    return out
+
+
+def sigmoid_gate_mul(a: torch.Tensor, packed: torch.Tensor, gate_column: int) -> torch.Tensor:
+    """a * sigmoid(gate), the gate lying in ``packed`` from column ``gate_column`` on; in place."""
+    _cuda(a, packed)
+    _contig(a, packed)
+    if a.dtype != packed.dtype or packed.shape[1] < gate_column + a.shape[1]:
+        raise KernelError("sigmoid_gate_mul: dtype or columns do not fit")
+    gate = packed.view(-1)[gate_column:]
+    rc = _gated().b200_sigmoid_gate_mul(_p(a), _p(a), ctypes.c_void_p(gate.data_ptr()), packed.shape[1], a.shape[0],
+                                        a.shape[1], _code(a), _stream())
+    _ok(rc, "sigmoid_gate_mul")
+    return a

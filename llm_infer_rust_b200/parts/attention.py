@@ -6,7 +6,7 @@ import math
 import torch
 
 from ..kernels import ops
-from .base import PagedKVSpec, ParamDecl, Part
+from .base import PagedKVSpec, ParamDecl, Part, StateSpec
 from .registry import register_part
 
 _KEYS_PER_CTA_AT_LEAST = 512      # fewer keys per CTA leave its warps' copy pipelines half empty
@@ -127,4 +127,119 @@ class GQAttention(Part):
         return ops.linear(out, p["o_proj"], lazy=True)
 
 
+class GatedConvAttention(Part):
+    """Grouped-query softmax attention over the paged cache whose q, k and v pass through a short causal
+    convolution over time, with soft-capped scores, values mixed with an earlier layer's and a sigmoid gate.
+
+    q, k, v, g = x W^T (one packed matrix: q rows, k rows, v rows, gate rows; keys are ``head_dim`` wide, values
+    ``v_head_dim``); then, each optional and a parameter of the part:
+      * ``conv_taps`` > 1: a causal convolution on every channel of q, k and v (``conv`` [channels, taps]; its
+        last taps - 1 inputs are the request's state);
+      * ``position_encoding``: half-split rotation of q and k;
+      * ``v_mix`` "source": this layer's v is kept for the step under the name ``v_mix_group``; "mix": v becomes
+        (1 - vmix) v + vmix v_source, and that is what the cache holds;
+      * ``softcap``: score <- cap * tanh(score / cap) after ``softmax_scale``;
+      * ``window``: only the last W keys are read;
+      * ``gate``: the heads' outputs are multiplied by sigmoid(g) before the output projection.
+    No bias."""
+    category = "mixer"
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = int(spec["hidden_size"])
+        self.nh = int(spec["num_heads"])
+        self.nkv = int(spec["num_kv_heads"])
+        self.d = int(spec["head_dim"])
+        self.dv = int(spec.get("v_head_dim") or self.d)
+        self.taps = int(spec.get("conv_taps") or 1)
+        self.window = spec.get("window")
+        self.scale = float(spec.get("softmax_scale", 1.0 / math.sqrt(self.d)))
+        self.softcap = float(spec.get("softcap") or 0.0)
+        self.gate = bool(spec.get("gate", True))
+        self.v_mix = spec.get("v_mix")                          # None | "source" | "mix"
+        self.v_mix_group = str(spec.get("v_mix_group", "v"))
+        if self.v_mix not in (None, "source", "mix"):
+            raise ValueError(f"v_mix {self.v_mix!r} is refused: source, mix or nothing")
+        if self.nh % self.nkv:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        for width in (self.d, self.dv):
+            if width % 2 or not 2 <= width <= 512:
+                raise ValueError(f"head size {width} is refused: the attention kernels take even head sizes up to 512")
+        if not 1 <= self.taps <= 8:
+            raise ValueError(f"{self.taps} taps are refused: the convolution kernels take 1 to 8")
+        name = spec.get("position_encoding")
+        self.rope = env.position_encodings[name] if name else None
+        if self.rope is not None and self.rope.rot_dim > self.d:
+            raise ValueError("the rotation is wider than a head")
+        self.qkv_channels = (self.nh + self.nkv) * self.d + self.nkv * self.dv
+
+    def param_decls(self):
+        rows = self.qkv_channels + (self.nh * self.dv if self.gate else 0)
+        decls = {"qkvg_proj": ParamDecl((rows, self.hidden)), "o_proj": ParamDecl((self.hidden, self.nh * self.dv))}
+        if self.taps > 1:
+            decls["conv"] = ParamDecl((self.qkv_channels, self.taps))
+        if self.v_mix is not None:
+            decls["vmix"] = ParamDecl((), "vector")
+        return decls
+
+    def bind(self, name, tensor):
+        super().bind(name, tensor)
+        if name == "conv":
+            self.params[name] = tensor.to(torch.float32).contiguous()
+        elif name == "vmix":
+            self.params[name] = tensor.to(torch.float32).reshape(1).contiguous()
+
+    def cache_spec(self):
+        return PagedKVSpec(self.nkv, self.d, self.window, self.dv if self.dv != self.d else None)
+
+    def state_spec(self):
+        return StateSpec((self.taps - 1, self.qkv_channels), torch.float32) if self.taps > 1 else None
+
+    def forward(self, x, ctx, cache):
+        p = self.params
+        tokens = x.shape[0]
+        rope = self.rope
+        packed = ops.linear(x, p["qkvg_proj"])
+        q = torch.empty((tokens, self.nh * self.d), dtype=packed.dtype, device=packed.device)
+        slots = ctx.slots[cache.group] if cache.writes else None
+        v_first, v_mode = None, 0
+        if self.v_mix == "source":
+            v_first = torch.empty((tokens, self.nkv * self.dv), dtype=torch.float32, device=packed.device)
+            ctx.extras["v_mix:" + self.v_mix_group] = v_first
+            v_mode = 1
+        elif self.v_mix == "mix":
+            v_first = ctx.extras.get("v_mix:" + self.v_mix_group)
+            if v_first is None or v_first.shape != (tokens, self.nkv * self.dv):
+                raise RuntimeError("a layer mixes its values with those of a layer that did not run in this step "
+                                   "(or whose values have another width)")
+            v_mode = 2
+        ops.conv_qkv_post(packed, p.get("conv"), cache.state, ctx, q, cache.k, cache.v,
+                          rope.inv_freq if rope else None, rope.rot_dim if rope else 0, slots, self.nh, self.nkv,
+                          self.d, self.dv, vmix=p.get("vmix") if v_mode == 2 else None, v_first=v_first, v_mode=v_mode)
+        if self.taps > 1:
+            ops.taps_state_update(packed, self.taps, self.qkv_channels, cache.state, ctx)
+        out = torch.empty((tokens, self.nh * self.dv), dtype=packed.dtype, device=packed.device)
+        g = cache.group
+        page = ctx.page_sizes[g]
+        if ctx.num_prefill:
+            ops.prefill_attention(q, cache.k, cache.v, out, ctx.block_tables[g], ctx.cu_q, ctx.kv_len,
+                                  ctx.prefix_len, ctx.prefill_rows, ctx.num_prefill, ctx.max_q_len,
+                                  self.nh, self.nkv, self.d, page, self.window, self.scale,
+                                  v_head_dim=self.dv, softcap=self.softcap)
+        if ctx.num_decode:
+            bound = min(ctx.kv_len_bound, self.window) if self.window else ctx.kv_len_bound
+            plain = self.dv == self.d and not self.softcap > 0.0
+            per_split = ops.decode_ctas_per_split(q.dtype, ctx.num_decode, self.nh, self.nkv, self.d, page, plain)
+            splits = decode_splits(per_split, bound, ctx.sm_count)
+            need = ops.decode_scratch_floats(ctx.num_decode, self.nh, max(self.d, self.dv), splits)
+            scratch = ctx.scratch(need) if need else None
+            ops.decode_attention(q, cache.k, cache.v, out, scratch, ctx.block_tables[g], ctx.cu_q,
+                                 ctx.kv_len, ctx.decode_rows, ctx.num_decode, self.nh, self.nkv, self.d,
+                                 page, self.window, self.scale, splits, v_head_dim=self.dv, softcap=self.softcap)
+        if self.gate:
+            ops.sigmoid_gate_mul(out, packed, self.qkv_channels)
+        return ops.linear(out, p["o_proj"])
+
+
 register_part("mixer", "gqa_attention", GQAttention)
+register_part("mixer", "gated_conv_attention", GatedConvAttention)

@@ -15,6 +15,8 @@ Categories and the interface each must have:
                       values it needs, or None); ``state_spec()`` (fixed-size
                       per-request state it needs, or None)
 ``feed_forward``      ``forward(x) -> y``
+``token_conv``        ``forward(x, scale, ctx, state, out_dtype) -> y`` (a convolution over time whose last
+                      inputs are per-request state); ``state_spec()``
 
 Optional, for fusion across parts: a norm may offer ``pending_add(x, residual, ...)``, which
 returns the add + norm unrun (``ops.PendingNorm``); a mixer, feed-forward or head that offers
@@ -46,6 +48,7 @@ class PagedKVSpec:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None     # None: all keys are kept; W: only the last W positions are read
+    v_head_dim: Optional[int] = None  # width of a value where it differs from a key's (None: head_dim)
 
 
 @dataclass(frozen=True)

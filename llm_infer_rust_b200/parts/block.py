@@ -67,4 +67,62 @@ class PreNormDeferredAdd:
         return self.feed_forward.forward(x), residual
 
 
+class PreNormInputConv:
+    """Pre-norm residual block over a float32 stream whose sublayers read their normed input through a short
+    causal convolution over time:
+
+        x <- x + mixer(conv_m(norm_in(x)));    x <- x + feed_forward(conv_f(norm_post(x)))
+
+    The stream x is float32 whatever the engine's dtype, and every sum into it is taken in float.  Parts by name:
+    ``input_norm``, ``mixer``, and optionally ``mixer_conv``, and (all or none) ``post_mixer_norm``,
+    ``feed_forward``, optionally ``ff_conv``; a layer without a feed-forward has only the first sublayer.  The
+    norms hand their scale on (``scale(x, add)``), the convolutions multiply by it as they read.  As in the
+    deferred-add block the last sublayer's output is not added here: the block returns (output, stream), and the
+    next block's first norm (or the model's final norm) adds it.  Each convolution keeps its last inputs in a
+    state of the block's own (``state_specs``), beside the mixer's."""
+    category = "block"
+
+    def __init__(self, layer_spec, env):
+        self.spec = layer_spec
+        self.env = env
+        parts = layer_spec.parts
+        self.input_norm = build_part("norm", layer_spec["input_norm"], env)
+        self.mixer = build_part("mixer", layer_spec["mixer"], env)
+        self.mixer_conv = build_part("token_conv", parts["mixer_conv"], env) if "mixer_conv" in parts else None
+        self.feed_forward = build_part("feed_forward", parts["feed_forward"], env) if "feed_forward" in parts else None
+        self.post_mixer_norm = self.ff_conv = None
+        if self.feed_forward is not None:
+            self.post_mixer_norm = build_part("norm", layer_spec["post_mixer_norm"], env)
+            self.ff_conv = build_part("token_conv", parts["ff_conv"], env) if "ff_conv" in parts else None
+
+    def children(self):
+        named = {"input_norm": self.input_norm, "mixer_conv": self.mixer_conv, "mixer": self.mixer,
+                 "post_mixer_norm": self.post_mixer_norm, "ff_conv": self.ff_conv, "feed_forward": self.feed_forward}
+        return {name: part for name, part in named.items() if part is not None}
+
+    def state_specs(self):
+        """Per-request states of the block itself, by name (the mixer's own is asked of the mixer)."""
+        specs = {}
+        for name, conv in (("mixer_conv", self.mixer_conv), ("ff_conv", self.ff_conv)):
+            if conv is not None and conv.state_spec() is not None:
+                specs[name] = conv.state_spec()
+        return specs
+
+    def _read(self, norm, conv, name, x, add, ctx, cache):
+        scale = norm.scale(x, add)                     # x += add, in float
+        if conv is None:
+            return ops.scaled_rows(x, scale, None, self.env.dtype)
+        return conv.forward(x, scale, ctx, cache.states.get(name), self.env.dtype)
+
+    def forward(self, h, residual, ctx, cache):
+        ops.flush_chain()
+        x, add = (h, None) if residual is None else (residual, h)
+        y = self.mixer.forward(self._read(self.input_norm, self.mixer_conv, "mixer_conv", x, add, ctx, cache), ctx, cache)
+        if self.feed_forward is None:
+            return y, x
+        y = self.feed_forward.forward(self._read(self.post_mixer_norm, self.ff_conv, "ff_conv", x, y, ctx, cache))
+        return y, x
+
+
 register_part("block", "pre_norm_deferred_add", PreNormDeferredAdd)
+register_part("block", "pre_norm_input_conv", PreNormInputConv)

@@ -9,19 +9,21 @@ from .registry import register_part
 
 
 class TokenEmbedding(Part):
-    """h[t] = table[ids[t]], unscaled (reference: src/layers/linear.rs:9-11)."""
+    """h[t] = table[ids[t]], unscaled (reference: src/layers/linear.rs:9-11).  ``out_dtype`` "float32": the
+    rows come out in float32 whatever the table's dtype (for a model whose residual stream is float32)."""
     category = "embedding"
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
         self.vocab = int(spec["vocab_size"])
         self.hidden = int(spec["hidden_size"])
+        self.out_dtype = torch.float32 if spec.get("out_dtype") == "float32" else env.dtype
 
     def param_decls(self):
         return {"weight": ParamDecl((self.vocab, self.hidden))}
 
     def forward(self, token_ids):
-        return ops.embedding(token_ids, self.params["weight"], self.env.dtype)
+        return ops.embedding(token_ids, self.params["weight"], self.out_dtype)
 
 
 class LinearHead(Part):

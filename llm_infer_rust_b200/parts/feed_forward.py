@@ -1,6 +1,8 @@
 """Feed-forward parts."""
 from __future__ import annotations
 
+import torch
+
 from ..kernels import ops
 from .base import ParamDecl, Part
 from .registry import register_part
@@ -42,4 +44,30 @@ class SwiGLU(Part):
         return ops.linear(ops.silu_mul(gate_up), self.params["down_proj"])
 
 
+class PolyNormFF(Part):
+    """down(act(up(x))) with act = PolyNorm: a N(z) + b N(z^2) + c N(z^3) + e, powers element by element, N the
+    division of a token's vector by its root mean square (in float).  ``act`` holds (a, b, c, e).  No bias."""
+    category = "feed_forward"
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = int(spec["hidden_size"])
+        self.inter = int(spec["intermediate_size"])
+        self.eps = float(spec["eps"])
+
+    def param_decls(self):
+        return {"up_proj": ParamDecl((self.inter, self.hidden)), "down_proj": ParamDecl((self.hidden, self.inter)),
+                "act": ParamDecl((4,), "vector")}
+
+    def bind(self, name, tensor):
+        super().bind(name, tensor)
+        if name == "act":
+            self.params[name] = tensor.to(torch.float32).contiguous()
+
+    def forward(self, x):
+        z = ops.linear(x, self.params["up_proj"])
+        return ops.linear(ops.poly_norm(z, self.params["act"], self.eps), self.params["down_proj"])
+
+
 register_part("feed_forward", "swiglu", SwiGLU)
+register_part("feed_forward", "poly_norm", PolyNormFF)

@@ -1,6 +1,8 @@
 """RMSNorm with an optional fused residual add."""
 from __future__ import annotations
 
+import torch
+
 from ..kernels import ops
 from .base import ParamDecl, Part
 from .registry import register_part
@@ -43,4 +45,36 @@ class RMSNorm(Part):
         return ops.PendingNorm(x, None, self.params["weight"], self.eps, rows=rows, write_residual=False)
 
 
+class ScalarRMSNorm(Part):
+    """y = x / sqrt(mean(x^2) + eps) * g with ONE gain g for all coordinates, over a float32 stream.
+
+    The norm is handed on as a per-token scale (``scale``: g / sqrt(mean(x^2) + eps), float32 [tokens]), so that
+    whatever reads the normed vector next (a convolution over time, a row gather for the head) multiplies as
+    it reads; ``scale`` can add a sublayer's output to the stream first, the sum in float.  ``forward`` is the
+    norm itself for chosen rows, rounded once to the engine's dtype."""
+    category = "norm"
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.eps = float(spec["eps"])
+
+    def param_decls(self):
+        return {"weight": ParamDecl((), "vector")}
+
+    def bind(self, name, tensor):
+        super().bind(name, tensor)
+        self.params[name] = tensor.to(torch.float32).reshape(1).contiguous()
+
+    def scale(self, x, add=None):
+        return ops.residual_scale(x, add, self.params["weight"], self.eps)
+
+    def forward(self, x, out=None, rows=None):
+        return ops.scaled_rows(x, self.scale(x), rows, self.env.dtype)
+
+    def forward_add(self, x, residual, out=None, rows=None, write_residual=True):
+        """The norm of residual + x for chosen rows; the sum stays in ``residual`` (the float32 stream)."""
+        return ops.scaled_rows(residual, self.scale(residual, x), rows, self.env.dtype)
+
+
 register_part("norm", "rms_norm", RMSNorm)
+register_part("norm", "scalar_rms_norm", ScalarRMSNorm)

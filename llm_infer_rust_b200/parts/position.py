@@ -34,4 +34,24 @@ class HalfSplitRope(Part):
         self.sin = torch.sin(angle).to(torch.float32).to(env.device).contiguous()
 
 
+class RotaryFrequencies(Part):
+    """Half-split rotary encoding without a table of positions: only the frequencies
+    f_i = theta^(-2i / rot_dim) / scaling_factor, i in [0, rot_dim / 2), as float32 (computed in float64).
+    A kernel that rotates forms the angle position * f_i in float and takes its cosine and sine itself, so
+    no longest position has to be known.  ``scaling_factor`` (linear scaling) divides every frequency."""
+    category = "position_encoding"
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.rot_dim = int(spec["rotary_dim"])
+        self.theta = float(spec["theta"])
+        self.scaling_factor = float(spec.get("scaling_factor", 1.0))
+        if self.rot_dim % 2 or self.rot_dim <= 0:
+            raise ValueError("rotary_dim must be even and positive")
+        i = torch.arange(0, self.rot_dim, 2, dtype=torch.float64)
+        inv_freq = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -i / self.rot_dim) / self.scaling_factor
+        self.inv_freq = inv_freq.to(torch.float32).to(env.device).contiguous()
+
+
 register_part("position_encoding", "half_split_rope", HalfSplitRope)
+register_part("position_encoding", "rotary_frequencies", RotaryFrequencies)

@@ -29,16 +29,23 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("--out", required=True)
     ap.add_argument("--max-tokens", type=int, required=True)
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--max-requests", type=int, default=4, help="state slots: requests that may be live at once")
     args = ap.parse_args(argv)
     os.makedirs(args.out, exist_ok=True)
 
+    from .config.registry import resolve_architecture
     from .engine import Engine, StepEntry
+    from .weights.loader import read_config_json
     page = args.page_size
     # Each live request's count is rounded up to a multiple of 64 (or of the page, if larger).
     unit = _round_up(64, page)
     pool_tokens = _round_up(max(args.max_tokens, unit), unit)
-    engine = Engine(args.model, dtype=args.dtype, max_running_req=8, page_size=page,
-                    max_total_tokens=pool_tokens, max_seq_len=None, cuda_graph_bs=0,
+    # A request may be as long as the pool (and the model) allows.
+    raw = read_config_json(args.model)
+    arch = resolve_architecture(raw)
+    longest = min(arch.model_spec(arch.parse_config(raw)).max_positions, max(8192, pool_tokens))
+    engine = Engine(args.model, dtype=args.dtype, max_running_req=args.max_requests, page_size=page,
+                    max_total_tokens=pool_tokens, max_seq_len=longest, cuda_graph_bs=0,
                     max_prefill_tokens_per_batch=0, chunked_prefill_size=0)
     ids: Dict[str, int] = {}
     next_id = 1

@@ -83,7 +83,7 @@ def counter_normal(seed: int, name: str, shape, device="cpu") -> torch.Tensor:
             for field in range(4):
                 total += _srl(h, 16 * field) & 0xFFFF
         out[at:at + i.numel()] = (total.to(torch.float32) - 8 * 32767.5) * _NORMAL_SCALE
-    return out.view(*[int(s) for s in shape])
+    return out.reshape(tuple(int(s) for s in shape))
 
 
 def _draw(src, seed: int, std: float, norm_std: float, device) -> torch.Tensor:
@@ -94,7 +94,7 @@ def _draw(src, seed: int, std: float, norm_std: float, device) -> torch.Tensor:
         for s in src.shape:
             n *= int(s)
         i = torch.arange(n, dtype=torch.int64, device=device)
-        return (_srl(_mix(key + i), 49)).to(torch.int32).view(*src.shape)          # 15 bits
+        return (_srl(_mix(key + i), 49)).to(torch.int32).reshape(tuple(src.shape))          # 15 bits
     z = counter_normal(seed, src.name, src.shape, device)
     if src.init == "norm":
         return 1.0 + norm_std * z if norm_std else torch.ones_like(z)
