@@ -26,6 +26,11 @@ decoded greedily, and the last K steps are timed.  One JSON line is printed:
 * ``routing``: which products of a decode step ran on this package's few-row kernels and which on the library (a
   rule of sizes, not a measurement: the same line again on the same machine takes the same kernels).
 
+``--design kefetar`` leaves all of the above aside and prints another line: prefill and decode throughput of Kefetar
+(gated convolutional attention and decay retention over a float32 stream) at two layer sizes, beside dense Qwen3 at
+the same width, heads, head size and parameter count, and every kernel of the new design alone beside the like
+kernel of Qwen3's path, each with its share of its roofline (``--design-sizes``, ``--layers``, default 8).
+
 Peaks come from MEASURED_PEAKS.json beside this file when it is there.  Weights are random
 (drawn on the device), token ids are synthetic.  One GPU only.
 """
@@ -289,6 +294,216 @@ def measure_point_shape(shape_name, context, steps, warmup, peak):
     return out, routing
 
 
+# ----------------------------------------------------------------------------- --design kefetar
+DESIGN_SIZES = {
+    "1k": dict(width=1024, heads=16, kv_heads=8, head_dim=128, inter=3072, vocab=151936),
+    "4k": dict(width=4096, heads=32, kv_heads=8, head_dim=128, inter=12288, vocab=151936),
+}
+
+
+def kefetar_config(size, layers):
+    """Attention and retention layers in turn, each with a feed-forward; the feed-forward is 1.5 x Qwen3's
+    intermediate size, which gives its two matrices the parameters of Qwen3's three."""
+    z = DESIGN_SIZES[size]
+    attn = {"type": "attention", "mlp": {"kind": "dense", "ff": z["inter"] * 3 // 2},
+            "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["head_dim"], "vdim": z["head_dim"],
+                      "conv": 3, "scale": z["head_dim"] ** -0.5, "softcap": 50.0, "v_mix": True,
+                      "rot": {"base": 1e6, "dims": z["head_dim"], "scaling": {"factor": 4.0}}}}
+    ret = {"type": "retention", "mlp": {"kind": "dense", "ff": z["inter"] * 3 // 2},
+           "mixer": {"heads": z["heads"], "dim": z["head_dim"], "vdim": z["head_dim"],
+                     "decay": [1.0 - 2.0 ** (-5 - 3 * h / max(1, z["heads"] - 1)) for h in range(z["heads"])],
+                     "rot": {"base": 1e6, "dims": z["head_dim"] // 2}}}
+    return {"architecture": "Kefetar", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
+            "canon": {"taps": 3}, "layers": [attn if i % 2 == 0 else ret for i in range(layers)]}
+
+
+def qwen3_config(size, layers):
+    z = DESIGN_SIZES[size]
+    return dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], rope_theta=1e6, rms_norm_eps=1e-6,
+                torch_dtype="bfloat16", eos_token_id=None, num_hidden_layers=layers, hidden_size=z["width"],
+                num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["head_dim"],
+                intermediate_size=z["inter"], vocab_size=z["vocab"], tie_word_embeddings=False,
+                max_position_embeddings=40960)
+
+
+def design_engine(raw, biggest, context, graphs=True):
+    from llm_infer_rust_b200.engine import Engine
+    return Engine(None, random_weights_config=raw, random_weights_seed=0, dtype="bfloat16", max_running_req=biggest,
+                  max_seq_len=context + 64, page_size=16, max_total_tokens=biggest * (context + 128) + 4096,
+                  cuda_graph_bs=biggest if graphs else 0, chunked_prefill_size=4096, log_level="warn")
+
+
+def timed_alone(fn, flush, repeats=7):
+    """Median device time in microseconds of one call of ``fn``, the second-level cache flushed before every call."""
+    import torch
+    for _ in range(3):
+        fn()
+    times = []
+    for _ in range(repeats):
+        flush.zero_()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        end.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(end) * 1e3)
+    return statistics.median(times)
+
+
+def kernel_table(size, peak):
+    """Every kernel of the new design alone, beside the like kernel of Qwen3's path, at one layer's sizes: a prompt
+    portion of 2,048 tokens and a decode step of 8 rows at 2,048 tokens.  ``frac``: bytes that must move / time / the
+    measured copy bandwidth, or FLOPs / time / the peak named in ``of``."""
+    import types
+    import torch
+    from llm_infer_rust_b200.kernels import ops
+    z = DESIGN_SIZES[size]
+    W, nh, nkv, d, F = z["width"], z["heads"], z["kv_heads"], z["head_dim"], z["inter"] * 3 // 2
+    dev, bf = torch.device("cuda"), torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    page, ctx_len, rows_dec = 16, 2048, 8
+    out = {}
+
+    def put(name, us, nbytes=None, flops=None, of="hbm"):
+        rec = {"us": round(us, 2)}
+        if nbytes is not None:
+            rec["gb_s"] = round(nbytes / us / 1e3, 1)
+            rec["frac"] = round(nbytes / us / 1e3 / peak["hbm_gbs"], 3)
+        if flops is not None:
+            top = {"bf16": peak["bf16_tflops"], "fp32": peak["fp32_tflops"]}[of]
+            rec["tflops"] = round(flops / us / 1e6, 2)
+            rec["frac"] = round(flops / us / 1e6 / top, 3)
+            rec["of"] = of
+        out[name] = rec
+
+    def step(rows):
+        cu, row_of, pos = [0], [], []
+        for r, (prefix, n) in enumerate(rows):
+            cu.append(cu[-1] + n)
+            row_of += [r] * n
+            pos += list(range(prefix, prefix + n))
+        R = len(rows)
+        width = -(-max(p + n for p, n in rows) // page)
+        table = torch.arange(1, R * width + 1, dtype=torch.int32, device=dev).view(R, width).contiguous()
+        slots = [int(table[r, (p + i) // page]) * page + (p + i) % page for r, (p, n) in enumerate(rows) for i in range(n)]
+        return types.SimpleNamespace(
+            num_rows=R, row_of_token=i32(row_of), cu_q=i32(cu), positions=i32(pos), prefix_len=i32([p for p, _ in rows]),
+            kv_len=i32([p + n for p, n in rows]), state_slots=i32(list(range(1, R + 1))), slots=i32(slots), table=table,
+            rows=i32(list(range(R))), tokens=cu[-1], pages=R * width + 1)
+
+    for phase, c in (("prefill", step([(0, ctx_len)])), ("decode", step([(ctx_len - 1, 1)] * rows_dec))):
+        T = c.tokens
+        x = torch.randn(T, W, device=dev)
+        y = torch.randn(T, W, device=dev).to(bf)
+        gain = torch.ones(1, device=dev)
+        res_b, xb = torch.randn(T, W, device=dev).to(bf), torch.randn(T, W, device=dev).to(bf)
+        wn = torch.ones(W, dtype=bf, device=dev)
+        # --- norm sites
+        scale = ops.residual_scale(x, y, gain, 1e-5)
+        put(f"{phase}.kefetar.residual_scale", timed_alone(lambda: ops.residual_scale(x, y, gain, 1e-5), flush), T * W * 10)
+        cw = torch.randn(W, 3, device=dev) * 0.1
+        cstate = torch.zeros(rows_dec + 1, 2, W, device=dev)
+        put(f"{phase}.kefetar.causal_taps", timed_alone(
+            lambda: ops.causal_taps(x, cw, cstate, c, bf, scale=scale, identity=True), flush), T * W * 6)
+        put(f"{phase}.qwen3.add_rms_norm", timed_alone(lambda: ops.add_rms_norm(xb, res_b, wn, 1e-6), flush), T * W * 8)
+        # --- between the projection and attention
+        cq = (nh + 2 * nkv) * d
+        packed = (torch.randn(T, cq + nh * d, device=dev) * 0.5).to(bf)
+        k_cache = torch.zeros(c.pages, nkv, page, d, dtype=bf, device=dev).normal_()
+        v_cache = torch.zeros(c.pages, nkv, page, d, dtype=bf, device=dev).normal_()
+        q = torch.empty(T, nh * d, dtype=bf, device=dev)
+        qw = torch.randn(cq, 3, device=dev) * 0.3
+        qstate = torch.zeros(rows_dec + 1, 2, cq, device=dev)
+        inv_freq = torch.pow(torch.tensor(1e6), -torch.arange(0, d, 2) / d).to(dev)
+        vfirst, lam = torch.randn(T, nkv * d, device=dev), torch.full((1,), 0.5, device=dev)
+        put(f"{phase}.kefetar.conv_qkv_post", timed_alone(lambda: (
+            ops.conv_qkv_post(packed, qw, qstate, c, q, k_cache, v_cache, inv_freq, d, c.slots, nh, nkv, d, d,
+                              vmix=lam, v_first=vfirst, v_mode=2),
+            ops.taps_state_update(packed, 3, cq, qstate, c)), flush), T * cq * 4 + T * nkv * d * 4)
+        qkv = packed[:, :cq].contiguous()
+        cos, sin = torch.ones(4096, d // 2, device=dev), torch.zeros(4096, d // 2, device=dev)
+        hn = torch.ones(d, dtype=bf, device=dev)
+        put(f"{phase}.qwen3.qkv_post", timed_alone(lambda: ops.qkv_post(
+            qkv, q, k_cache, v_cache, hn, hn, 1e-6, cos, sin, d, c.positions, c.slots, nh, nkv, d), flush), T * cq * 4)
+        # --- attention
+        o = torch.empty(T, nh * d, dtype=bf, device=dev)
+        if phase == "prefill":
+            fl = 4.0 * nh * d * T * (T + 1) / 2
+            put("prefill.kefetar.attention_softcap", timed_alone(lambda: ops.prefill_attention(
+                q, k_cache, v_cache, o, c.table, c.cu_q, c.kv_len, c.prefix_len, c.rows, 1, T, nh, nkv, d, page, None,
+                d ** -0.5, v_head_dim=d, softcap=50.0, precise_weights=True), flush, repeats=3), flops=fl, of="bf16")
+            put("prefill.qwen3.attention", timed_alone(lambda: ops.prefill_attention(
+                q, k_cache, v_cache, o, c.table, c.cu_q, c.kv_len, c.prefix_len, c.rows, 1, T, nh, nkv, d, page, None,
+                d ** -0.5), flush), flops=fl, of="bf16")
+        else:
+            from llm_infer_rust_b200.parts.attention import decode_splits
+            kvb = rows_dec * ctx_len * nkv * d * 2 * 2
+            for name, kw, plain in (("kefetar.attention_softcap", dict(v_head_dim=d, softcap=50.0, precise_weights=True), True),
+                                    ("qwen3.attention", {}, True)):
+                splits = decode_splits(ops.decode_ctas_per_split(bf, rows_dec, nh, nkv, d, page, plain), ctx_len, 148)
+                need = ops.decode_scratch_floats(rows_dec, nh, d, splits)
+                scratch = torch.empty(max(need, 1), device=dev)
+                put(f"decode.{name}", timed_alone(lambda: ops.decode_attention(
+                    q, k_cache, v_cache, o, scratch, c.table, c.cu_q, c.kv_len, c.rows, rows_dec, nh, nkv, d, page, None,
+                    d ** -0.5, splits, **kw), flush), kvb)
+        # --- gates and activations
+        put(f"{phase}.kefetar.sigmoid_gate_mul", timed_alone(lambda: ops.sigmoid_gate_mul(o, packed, cq), flush), T * nh * d * 6)
+        zf = (torch.randn(T, F, device=dev)).to(bf)
+        coef = torch.ones(4, device=dev)
+        put(f"{phase}.kefetar.poly_norm", timed_alone(lambda: ops.poly_norm(zf, coef, 1e-5), flush), T * F * 4)
+        gu = torch.randn(T, 2 * z["inter"], device=dev).to(bf)
+        put(f"{phase}.qwen3.silu_mul", timed_alone(lambda: ops.silu_mul(gu), flush), T * z["inter"] * 6)
+        # --- retention
+        rp = (torch.randn(T, nh * 4 * d, device=dev) * 0.3).to(bf)
+        rstate = torch.zeros(rows_dec + 1, nh, d, d, device=dev)
+        decay = torch.full((nh,), 0.99, device=dev)
+        rf = inv_freq[: d // 4].contiguous()
+        us = timed_alone(lambda: ops.retention(rp, rstate, decay, rf, d // 2, d ** -0.5, c, nh, d, d), flush,
+                         repeats=3 if phase == "prefill" else 7)
+        if phase == "prefill":
+            put("prefill.kefetar.retention", us, flops=4.0 * T * nh * d * d, of="fp32")
+        else:
+            put("decode.kefetar.retention", us, rows_dec * nh * d * d * 8)
+        ro = torch.randn(T, nh * d, device=dev)
+        put(f"{phase}.kefetar.head_unit_norm_gate", timed_alone(
+            lambda: ops.head_unit_norm_gate(ro, rp, nh * 3 * d, nh, d, 1e-5), flush), T * nh * d * 8)
+    return out
+
+
+def design_main(args) -> int:
+    import torch
+    peak, peak_source = peaks()
+    # float32 FMA throughput of the device: SMs x 128 lanes x 2 x the highest SM clock
+    props = torch.cuda.get_device_properties(0)
+    peak["fp32_tflops"] = props.multi_processor_count * 128 * 2 * 1.965e9 / 1e12
+    context, line = args.context, {"design": "kefetar", "layers": args.layers or 8, "context": args.context,
+                                   "dtype": "bf16", "data": "synthetic token ids, random weights", "peaks": peak_source,
+                                   "sizes": {}, "kernels": {}}
+    for size in [n for n in args.design_sizes.split(",") if n]:
+        rec = {}
+        for name, raw in (("kefetar", kefetar_config(size, args.layers or 8)), ("qwen3", qwen3_config(size, args.layers or 8))):
+            engine = design_engine(raw, 8, context)
+            vocab = raw.get("vocab", raw.get("vocab_size"))
+            ms = prefill_timed(engine, 2048, vocab)
+            one = {"params_m": round(engine.model.parameter_bytes() / 2e6, 1), "prefill_tok_s": round(2048e3 / ms, 1),
+                   "prefill_ms": round(ms, 3)}
+            for b in (1, 8):
+                run = decode_device_timed(engine, b, context, max(8, args.steps // 4), args.warmup, vocab)
+                one[f"decode_b{b}_tok_s"] = round(run["tokens_per_s"], 1)
+                one[f"decode_b{b}_ms"] = round(run["ms_per_step"], 4)
+                one[f"decode_b{b}_launches_per_step"] = run["launches"] // max(8, args.steps // 4)
+            rec[name] = one
+            del engine
+            release()
+        line["sizes"][size] = rec
+        if not args.no_kernels:
+            line["kernels"][size] = kernel_table(size, peak)
+            release()
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -304,7 +519,19 @@ def main() -> int:
                     help="other shapes measured into `points` (decode at batch 1 / 8 / 64, prefill), comma separated")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one phase alone and print a short line (for profiling)")
+    ap.add_argument("--design", choices=["qwen3", "kefetar"], default="qwen3",
+                    help="kefetar: the new design beside Qwen3 at equal sizes, and its kernels alone (another line)")
+    ap.add_argument("--design-sizes", default="1k,4k", help="layer sizes of --design kefetar, comma separated")
+    ap.add_argument("--no-kernels", action="store_true", help="--design kefetar without the table of single kernels")
     args = ap.parse_args()
+    if args.design == "kefetar" and args.impl == "ours":
+        if args.gpus != 1:
+            print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+            return 2
+        args.warmup = max(args.warmup, 3)
+        if args.context == 4096:
+            args.context = 2048
+        return design_main(args)
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return 0

@@ -9,7 +9,7 @@
                    {"kind": "dense", "ff": F})
 
     attention mixer: heads, kv_heads, dim (query / key size), vdim (value size), scale, and optionally conv
-                   (taps of the convolution on q, k, v), rot {base, dims, scaling {factor}}, softcap, v_mix, window
+                   (taps of the convolution on q, k, v), rot {base, dims, scaling {factor}}, softcap, v_mix
     retention mixer: heads, dim, vdim, decay (one number per head), optionally rot {base, dims, scaling {factor}}
 
 Nothing here is a default for a size: a key that the design needs and the file lacks is an error.
@@ -67,7 +67,6 @@ class KefetarLayer:
     scale: float = 1.0
     softcap: Optional[float] = None
     v_mix: bool = False
-    window: Optional[int] = None
     # retention
     decay: Tuple[float, ...] = ()
 
@@ -146,8 +145,7 @@ class KefetarConfig:
                     conv=_int(m, "conv", where + "mixer.") if m.get("conv") is not None else 1,
                     scale=_number(m, "scale", where + "mixer."),
                     softcap=_number(m, "softcap", where + "mixer.") if m.get("softcap") is not None else None,
-                    v_mix=bool(m.get("v_mix", False)),
-                    window=_int(m, "window", where + "mixer.") if m.get("window") is not None else None))
+                    v_mix=bool(m.get("v_mix", False))))
             elif kind == "retention":
                 decay = m.get("decay")
                 if not isinstance(decay, list) or len(decay) != heads or any(
@@ -191,7 +189,7 @@ class KefetarConfig:
                 mixer = PartSpec("gated_conv_attention", {
                     "hidden_size": self.width, "num_heads": l.heads, "num_kv_heads": l.kv_heads, "head_dim": l.dim,
                     "v_head_dim": l.vdim, "conv_taps": l.conv, "softmax_scale": l.scale, "softcap": l.softcap,
-                    "window": l.window, "gate": True, "v_mix": role, "v_mix_group": "first",
+                    "window": None, "gate": True, "v_mix": role, "v_mix_group": "first",
                     "position_encoding": encoding(l.rot)})
             else:
                 mixer = PartSpec("decay_retention", {

@@ -68,6 +68,25 @@ __device__ __forceinline__ float fast_exp2(float x) {      // 2^x in one special
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
 }
+// How a raw score q.k becomes the exponent of 2 that the softmax takes: score * scale_log2, or, with a soft-cap,
+// cap_log2 * tanh(score * tanh_in) (cap_log2 = cap * log2(e), tanh_in = scale / cap; cap_log2 <= 0: no cap).
+// split_p: the weights enter P.V as two bfloat16 terms, the rounded weight and what the rounding left, so that
+// the product carries the weights to about 16 bits instead of 8.
+struct ScoreForm {
+  float scale_log2, tanh_in, cap_log2;
+  int split_p;
+};
+__device__ __forceinline__ float tanh_by_exp2(float x) {     // 1 - 2 / (e^(2x) + 1): absolute error about 1e-7
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(e) : "f"(x * 2.8853900817779268f));
+  return 1.0f - __fdividef(2.0f, e + 1.0f);
+}
+__device__ __forceinline__ uint32_t pack_bf16_rest(float lo, float hi, uint32_t& rest) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  const __nv_bfloat162 r = __floats2bfloat162_rn(lo - __low2float(v), hi - __high2float(v));
+  rest = *reinterpret_cast<const uint32_t*>(&r);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -133,11 +152,11 @@ struct WarpAcc {
 };
 
 // One block of 32 keys against the 16 query rows in `qs`.  `qpos0/1`: position of the query in rows
-// lane/4 and lane/4 + 8 (-1: the row is unused).  `scale_log2` = softmax scale * log2(e).
+// lane/4 and lane/4 + 8 (-1: the row is unused).  `sf`: scale, soft-cap and the form of the weights (ScoreForm).
 // MASKED = false: the caller knows that every key of the block is visible to every used row of the warp.
 template <bool MASKED>
 __device__ __forceinline__ void block_mma(const bf16* qs, const unsigned char* ks, const unsigned char* vs, int first_key, int kv_end,
-                                          int window, int qpos0, int qpos1, float scale_log2, WarpAcc& st) {
+                                          int window, int qpos0, int qpos1, const ScoreForm& sf, WarpAcc& st) {
   const int lane = threadIdx.x & 31;
   const int mi = lane >> 3, r8 = lane & 7;
   float s[4][4];
@@ -168,8 +187,13 @@ __device__ __forceinline__ void block_mma(const bf16* qs, const unsigned char* k
         v0 = in_seq && v0 && key <= qpos0 && (window <= 0 || key > qpos0 - window);
         v1 = in_seq && v1 && key <= qpos1 && (window <= 0 || key > qpos1 - window);
       }
-      s[n][e] = v0 ? s[n][e] * scale_log2 : -INFINITY;
-      s[n][2 + e] = v1 ? s[n][2 + e] * scale_log2 : -INFINITY;
+      float a0 = s[n][e] * sf.scale_log2, a1 = s[n][2 + e] * sf.scale_log2;
+      if (sf.cap_log2 > 0.0f) {
+        a0 = sf.cap_log2 * tanh_by_exp2(s[n][e] * sf.tanh_in);
+        a1 = sf.cap_log2 * tanh_by_exp2(s[n][2 + e] * sf.tanh_in);
+      }
+      s[n][e] = v0 ? a0 : -INFINITY;
+      s[n][2 + e] = v1 ? a1 : -INFINITY;
       mx0 = fmaxf(mx0, s[n][e]);
       mx1 = fmaxf(mx1, s[n][2 + e]);
     }
@@ -200,17 +224,21 @@ __device__ __forceinline__ void block_mma(const bf16* qs, const unsigned char* k
   }
 #pragma unroll
   for (int kk = 0; kk < 2; ++kk) {
-    uint32_t a[4];
-    a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-    a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-    a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-    a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+    uint32_t a[4], rest[4];
+    a[0] = pack_bf16_rest(s[2 * kk][0], s[2 * kk][1], rest[0]);
+    a[1] = pack_bf16_rest(s[2 * kk][2], s[2 * kk][3], rest[1]);
+    a[2] = pack_bf16_rest(s[2 * kk + 1][0], s[2 * kk + 1][1], rest[2]);
+    a[3] = pack_bf16_rest(s[2 * kk + 1][2], s[2 * kk + 1][3], rest[3]);
 #pragma unroll
     for (int dn = 0; dn < D / 8; dn += 2) {
       uint32_t b[4];
       ldmatrix_x4_trans(b, vs + swz(kk * 16 + (mi & 1) * 8 + r8, dn + (mi >> 1)));
       mma_bf16(st.o[dn], a, b[0], b[1]);
       mma_bf16(st.o[dn + 1], a, b[2], b[3]);
+      if (sf.split_p) {
+        mma_bf16(st.o[dn], rest, b[0], b[1]);
+        mma_bf16(st.o[dn + 1], rest, b[2], b[3]);
+      }
     }
   }
 }
@@ -225,7 +253,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                   const bf16* __restrict__ q, bf16* __restrict__ out, float* __restrict__ part_acc,
                   float* __restrict__ part_ml, const int* __restrict__ block_table, int table_stride,
                   const int* __restrict__ cu_q, const int* __restrict__ kv_len, const int* __restrict__ rows, int nh,
-                  int nkv, int page_size, int box_rows, int window, float scale_log2, int cluster_merge, int* err) {
+                  int nkv, int page_size, int box_rows, int window, ScoreForm sf, int cluster_merge, int* err) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   bf16* qs = reinterpret_cast<bf16*>(tiles + static_cast<size_t>(WARPS) * STAGES * TILE_BYTES);   // [16][LD]
@@ -313,9 +341,9 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     }
     __syncwarp();
     if (first_key + KB <= kv_end && (window <= 0 || first_key > qp - window))
-      block_mma<false>(qs, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos0, qpos1, scale_log2, st);
+      block_mma<false>(qs, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos0, qpos1, sf, st);
     else
-      block_mma<true>(qs, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos0, qpos1, scale_log2, st);
+      block_mma<true>(qs, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos0, qpos1, sf, st);
     __syncwarp();                                      // every lane is done reading before the stage is refilled
     if (++stage == STAGES) { stage = 0; parity ^= 1u; }
   }
@@ -439,7 +467,7 @@ prefill_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
                    const bf16* __restrict__ q, bf16* __restrict__ out, const int* __restrict__ block_table,
                    int table_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                    const int* __restrict__ prefix_len, const int* __restrict__ rows, int nh, int nkv, int page_size,
-                   int box_rows, int window, float scale_log2, int* err) {
+                   int box_rows, int window, ScoreForm sf, int* err) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   bf16* qs = reinterpret_cast<bf16*>(tiles + static_cast<size_t>(STAGES) * TILE_BYTES);     // [PF_ROWS][LD]
@@ -543,9 +571,9 @@ prefill_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
       const bool all_visible = first_key + KB - 1 <= p_lo + w_tok_lo && first_key + KB <= kv_end &&
                                (window <= 0 || first_key > w_p_hi - window);
       if (all_visible)
-        block_mma<false>(my_q, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos[0], qpos[1], scale_log2, st);
+        block_mma<false>(my_q, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos[0], qpos[1], sf, st);
       else
-        block_mma<true>(my_q, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos[0], qpos[1], scale_log2, st);
+        block_mma<true>(my_q, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos[0], qpos[1], sf, st);
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(empty + s);
@@ -618,6 +646,15 @@ B200_EXPORT int b200_kv_tensor_map(void* out_map, const void* cache, long long r
   return 0;
 }
 
+static ScoreForm score_form(float scale, float softcap, int split_p) {
+  ScoreForm sf;
+  sf.scale_log2 = scale * 1.4426950408889634f;
+  sf.tanh_in = softcap > 0.0f ? scale / softcap : 0.0f;
+  sf.cap_log2 = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f;
+  sf.split_p = split_p;
+  return sf;
+}
+
 // Decoded tokens over a bfloat16 cache.  `k_map`, `v_map`: descriptors from b200_kv_tensor_map with
 // box_rows = min(page_size, 32); page_size must be a power of two; at most 16 query heads per KV head.
 // `scratch` as for b200_decode_attention of attention.cu.
@@ -625,7 +662,7 @@ B200_EXPORT int b200_decode_attention_mma(const void* q, const void* k_map, cons
                                           float* scratch, const int* block_table, int table_stride,
                                           const int* cu_q, const int* kv_len, const int* rows, int n_rows, int nh,
                                           int nkv, int page_size, int window, float scale, int splits,
-                                          int* err, cudaStream_t stream) {
+                                          float softcap, int split_p, int* err, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || nh / nkv > QROWS || page_size <= 0 || splits <= 0) return B200_BAD_SIZE;
   if ((page_size & (page_size - 1)) != 0) return B200_BAD_SIZE;
@@ -660,8 +697,8 @@ B200_EXPORT int b200_decode_attention_mma(const void* q, const void* k_map, cons
                              static_cast<long long>(splits) * nkv * n_rows <= sm_count;
   int rc = b200_launch(decode_mma_kernel<kWarps, kStages>, grid, dim3(kWarps * 32), smem, stream, cluster_merge ? splits : 0,
                        kmap, vmap, static_cast<const bf16*>(q), static_cast<bf16*>(out), part_acc, part_ml, block_table,
-                       table_stride, cu_q, kv_len, rows, nh, nkv, page_size, box_rows, window, scale * 1.4426950408889634f,
-                       cluster_merge ? 1 : 0, err);
+                       table_stride, cu_q, kv_len, rows, nh, nkv, page_size, box_rows, window,
+                       score_form(scale, softcap, split_p), cluster_merge ? 1 : 0, err);
   if (rc != 0 || splits == 1 || cluster_merge) return rc;
   dim3 mgrid(n_rows, nh);
   return b200_launch(decode_mma_merge_kernel, mgrid, dim3(D >= 128 ? 128 : 64), 0, stream, 0, static_cast<bf16*>(out),
@@ -679,7 +716,7 @@ B200_EXPORT int b200_prefill_attention_mma(const void* q, const void* k_map, con
                                            const int* block_table, int table_stride, const int* cu_q,
                                            const int* kv_len, const int* prefix_len, const int* rows, int n_rows,
                                            int max_q_len, int nh, int nkv, int page_size, int window, float scale,
-                                           int* err, cudaStream_t stream) {
+                                           float softcap, int split_p, int* err, cudaStream_t stream) {
   if (n_rows <= 0 || max_q_len <= 0) return 0;
   if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || nh / nkv > QROWS || page_size <= 0) return B200_BAD_SIZE;
   if ((page_size & (page_size - 1)) != 0) return B200_BAD_SIZE;
@@ -701,6 +738,6 @@ B200_EXPORT int b200_prefill_attention_mma(const void* q, const void* k_map, con
   dim3 grid(nkv, n_rows, n_tiles);
   prefill_mma_kernel<kPfStages><<<grid, PF_WARPS * 32, smem, stream>>>(
       kmap, vmap, static_cast<const bf16*>(q), static_cast<bf16*>(out), block_table, table_stride, cu_q, kv_len,
-      prefix_len, rows, nh, nkv, page_size, box_rows, window, scale * 1.4426950408889634f, err);
+      prefix_len, rows, nh, nkv, page_size, box_rows, window, score_form(scale, softcap, split_p), err);
   return b200_check_launch();
 }

@@ -66,6 +66,125 @@ conv_qkv_post_kernel(TapsInput<T> in, T* __restrict__ q_out, T* __restrict__ k_c
   }
 }
 
+// ------------------------------------------------------------------ eight channels a thread
+// The same result for sizes whose rows are whole 16-byte pieces (d, dv, rot_dim / 2 and the rows of `x` multiples
+// of 8): a thread takes 8 consecutive channels, and in the rotated part of a head also their 8 partners, so that
+// every channel passes the convolution once and every pair takes one sine and cosine.  A head has
+// rot_dim / 16 paired items and (d - rot_dim) / 8 single ones; v has dv / 8 single items per head.
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const float* v) {
+  if constexpr (sizeof(T) == 4) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  } else {
+    uint4 u;
+    __nv_bfloat162 h;
+    h = __floats2bfloat162_rn(v[0], v[1]); u.x = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2bfloat162_rn(v[2], v[3]); u.y = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2bfloat162_rn(v[4], v[5]); u.z = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2bfloat162_rn(v[6], v[7]); u.w = *reinterpret_cast<uint32_t*>(&h);
+    *reinterpret_cast<uint4*>(p) = u;
+  }
+}
+
+// y[0..8) = the convolution's outputs of channels c .. c + 7 of token t
+template <typename T>
+__device__ __forceinline__ void taps_value8(const TapsInput<T>& in, const TapsRow& row, int t, int c, float* y) {
+  float u[8];
+  load_floats<T, 8>(in.x + static_cast<size_t>(t) * in.in_stride + c, u);
+  if (in.w == nullptr) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) y[i] = u[i];
+    return;
+  }
+  const int taps = in.taps;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) y[i] = in.w[static_cast<size_t>(c + i) * taps + taps - 1] * u[i];
+  for (int back = 1; back < taps; ++back) {
+    if (back <= row.local) {
+      load_floats<T, 8>(in.x + static_cast<size_t>(t - back) * in.in_stride + c, u);
+    } else if (row.has_past) {
+      load_floats<float, 8>(row.state + static_cast<size_t>(taps - 1 - (back - row.local)) * in.channels + c, u);
+    } else {
+      continue;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) y[i] = fmaf(in.w[static_cast<size_t>(c + i) * taps + taps - 1 - back], u[i], y[i]);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+conv_qkv_post_vec_kernel(TapsInput<T> in, T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                         const float* __restrict__ inv_freq, int rot_dim, const int* __restrict__ positions,
+                         const int* __restrict__ slots, int nh, int nkv, int d, int dv, int page_size,
+                         long long cache_slots, const float* __restrict__ vmix, float* __restrict__ v_first,
+                         int v_mode, int* __restrict__ err) {
+  const int t = blockIdx.x;
+  const int item = blockIdx.y * blockDim.x + threadIdx.x;
+  const int half = rot_dim >> 1;
+  const int per_head = half / 8 + (d - rot_dim) / 8;
+  const int qk_items = (nh + nkv) * per_head;
+  if (item >= qk_items + nkv * (dv / 8)) return;
+  const TapsRow row = taps_row(in, t);
+  const int cq = nh * d, ck = nkv * d;
+  int slot = -1, page = 0, off = 0;
+  if (slots != nullptr) {
+    slot = slots[t];
+    if (slot < 0 || slot >= cache_slots) {
+      if (item == 0) atomicOr(err, B200_ERR_SLOT_RANGE);
+      slot = -1;
+    } else {
+      page = slot / page_size;
+      off = slot - page * page_size;
+    }
+  }
+  float a[8], b[8];
+  if (item < qk_items) {
+    const int head = item / per_head, part = item - head * per_head;          // q heads first, then k heads
+    const bool paired = part < half / 8;
+    const int e = paired ? part * 8 : rot_dim + (part - half / 8) * 8;
+    const int c = head * d + e;                                               // (q and k channels are contiguous)
+    taps_value8(in, row, t, c, a);
+    if (paired) {
+      taps_value8(in, row, t, c + half, b);
+      const float pos = static_cast<float>(positions[t]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float sn, cs;
+        sincosf(pos * inv_freq[e + i], &sn, &cs);
+        const float lo = a[i] * cs - b[i] * sn, hi = b[i] * cs + a[i] * sn;
+        a[i] = lo; b[i] = hi;
+      }
+    }
+    T* dst;
+    if (head < nh) {
+      dst = q_out + static_cast<size_t>(t) * cq + c;
+    } else {
+      if (slot < 0) return;
+      dst = k_cache + ((static_cast<size_t>(page) * nkv + (head - nh)) * page_size + off) * d + e;
+    }
+    store8<T>(dst, a);
+    if (paired) store8<T>(dst + half, b);
+    return;
+  }
+  const int vi = item - qk_items;
+  const int kvh = vi / (dv / 8), e = (vi - kvh * (dv / 8)) * 8;
+  taps_value8(in, row, t, cq + ck + kvh * dv + e, a);
+  float* vf = v_first + static_cast<size_t>(t) * (nkv * dv) + kvh * dv + e;
+  if (v_mode == 1) {
+    *reinterpret_cast<float4*>(vf) = make_float4(a[0], a[1], a[2], a[3]);
+    *reinterpret_cast<float4*>(vf + 4) = make_float4(a[4], a[5], a[6], a[7]);
+  } else if (v_mode == 2) {
+    const float lam = vmix[0];
+    load_floats<float, 8>(vf, b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a[i] = (1.0f - lam) * a[i] + lam * b[i];
+  }
+  if (slot < 0) return;
+  store8<T>(v_cache + ((static_cast<size_t>(page) * nkv + kvh) * page_size + off) * dv + e, a);
+}
+
 template <typename T>
 static int launch(const void* x, int in_stride, const float* w, int taps, float* state, const int* row_of_token,
                   const int* cu_q, const int* prefix_len, const int* state_slots, void* q_out, void* k_cache,
@@ -76,6 +195,19 @@ static int launch(const void* x, int in_stride, const float* w, int taps, float*
   in.x = static_cast<const T*>(x); in.in_stride = in_stride; in.scale = nullptr; in.w = w; in.taps = w ? taps : 1;
   in.channels = nh * d + nkv * d + nkv * dv; in.state = state; in.row_of_token = row_of_token; in.cu_q = cu_q;
   in.prefix_len = prefix_len; in.state_slots = state_slots;
+  const int half = rot_dim / 2;
+  const bool aligned = (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(q_out) |
+                        reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
+                        reinterpret_cast<uintptr_t>(state) | reinterpret_cast<uintptr_t>(v_first)) % 16 == 0;
+  if (aligned && d % 8 == 0 && dv % 8 == 0 && half % 8 == 0 && in_stride % 8 == 0) {
+    const int items = (nh + nkv) * (half / 8 + (d - rot_dim) / 8) + nkv * (dv / 8);
+    const dim3 vgrid(tokens, (items + 127) / 128);
+    conv_qkv_post_vec_kernel<T><<<vgrid, 128, 0, stream>>>(in, static_cast<T*>(q_out), static_cast<T*>(k_cache),
+                                                           static_cast<T*>(v_cache), inv_freq, rot_dim, positions, slots,
+                                                           nh, nkv, d, dv, page_size, cache_slots, vmix, v_first, v_mode,
+                                                           err);
+    return b200_check_launch();
+  }
   const dim3 grid(tokens, (in.channels + 255) / 256);
   conv_qkv_post_kernel<T><<<grid, 256, 0, stream>>>(in, static_cast<T*>(q_out), static_cast<T*>(k_cache),
                                                     static_cast<T*>(v_cache), inv_freq, rot_dim, positions, slots, nh,

@@ -146,6 +146,250 @@ static int dispatch_scan(const void* x, int in_stride, float* o, float* state, c
   return B200_BAD_SIZE;
 }
 
+// ------------------------------------------------------------------ prompt portions, in chunks of 64 tokens
+// Three kernels.  (1) retention_rotate_kernel: q and k of every token rotated once (k also scaled) into float
+// buffers qf, kf [tokens, heads * d].  (2) retention_state_kernel: grid (rows, heads, 32 x 32 tiles of the
+// state); a block walks its row's chunks in order, leaves its tile of the state as it stood BEFORE each chunk in
+// `before` [chunk slot, heads, d, dv], runs the recurrence S <- decay S + k v^T over the chunk's tokens one by
+// one, and writes the row's final state.  (3) retention_chunk_kernel: grid (chunk slots, heads), every chunk on
+// its own:   o_i = decay^(i+1) q_i^T S_before + sum over j <= i of decay^(i-j) (q_i . k_j) v_j
+// as two small float products in shared memory (A = Q K^T with the decays, then [A | Q diag] [V ; S_before]).
+// Chunk slots of row r start at chunk_base[r] (a prefix sum on the device, made by retention_chunk_base_kernel).
+constexpr int RC = 64;         // tokens of a chunk
+constexpr int RD = 128;        // widest head (keys and values) of the chunked path
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+retention_rotate_kernel(const T* __restrict__ x, int in_stride, float* __restrict__ qf, float* __restrict__ kf,
+                        const float* __restrict__ inv_freq, int rot_dim, float k_scale,
+                        const int* __restrict__ positions, int heads, int d) {
+  const int t = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int hd = heads * d;
+  if (c >= 2 * hd) return;
+  const bool is_k = c >= hd;
+  const int cc = is_k ? c - hd : c;
+  const int h = cc / d, e = cc - h * d;
+  const T* src = x + static_cast<size_t>(t) * in_stride + (is_k ? hd : 0) + h * d;
+  const float y = rotated<T>(src, e, rot_dim, static_cast<float>(positions[t]), inv_freq);
+  (is_k ? kf : qf)[static_cast<size_t>(t) * hd + cc] = is_k ? y * k_scale : y;
+}
+
+__global__ void retention_chunk_base_kernel(const int* __restrict__ cu_q, int num_rows, int* __restrict__ chunk_base) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    int at = 0;
+    for (int r = 0; r < num_rows; ++r) {
+      chunk_base[r] = at;
+      at += (cu_q[r + 1] - cu_q[r] + RC - 1) / RC;
+    }
+    chunk_base[num_rows] = at;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+retention_state_kernel(const T* __restrict__ x, int in_stride, const float* __restrict__ kf, float* __restrict__ before,
+                       float* __restrict__ state, const float* __restrict__ decay, const int* __restrict__ cu_q,
+                       const int* __restrict__ prefix_len, const int* __restrict__ state_slots,
+                       const int* __restrict__ chunk_base, int heads, int d, int dv) {
+  __shared__ float ks[RC][33];
+  __shared__ float vs[RC][33];
+  const int r = blockIdx.x, h = blockIdx.y;
+  const int tiles_v = (dv + 31) / 32;
+  const int ti = blockIdx.z / tiles_v, tj = blockIdx.z - ti * tiles_v;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;            // column, and rows ty + 8 m
+  const int col = tj * 32 + tx;
+  const int first = cu_q[r], n = cu_q[r + 1] - first;
+  const float g = decay[h];
+  float* st = state + (static_cast<size_t>(state_slots[r]) * heads + h) * d * dv;
+  const bool has_past = prefix_len[r] > 0;
+  const int voff = 2 * heads * d + h * dv;
+  float S[4];
+#pragma unroll
+  for (int m = 0; m < 4; ++m) {
+    const int i = ti * 32 + ty + 8 * m;
+    S[m] = (has_past && i < d && col < dv) ? st[static_cast<size_t>(i) * dv + col] : 0.0f;
+  }
+  for (int base = 0, c = chunk_base[r]; base < n; base += RC, ++c) {
+    const int L = min(RC, n - base);
+    for (int idx = threadIdx.x; idx < L * 32; idx += blockDim.x) {
+      const int j = idx >> 5, e = idx & 31;
+      const int t = first + base + j;
+      ks[j][e] = ti * 32 + e < d ? kf[static_cast<size_t>(t) * heads * d + h * d + ti * 32 + e] : 0.0f;
+      vs[j][e] = tj * 32 + e < dv ? to_f32<T>(x[static_cast<size_t>(t) * in_stride + voff + tj * 32 + e]) : 0.0f;
+    }
+    float* dst = before + (static_cast<size_t>(c) * heads + h) * d * dv;
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+      const int i = ti * 32 + ty + 8 * m;
+      if (i < d && col < dv) dst[static_cast<size_t>(i) * dv + col] = S[m];
+    }
+    __syncthreads();
+    for (int j = 0; j < L; ++j) {
+      const float v = vs[j][tx];
+#pragma unroll
+      for (int m = 0; m < 4; ++m) S[m] = fmaf(g, S[m], ks[j][ty + 8 * m] * v);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int m = 0; m < 4; ++m) {
+    const int i = ti * 32 + ty + 8 * m;
+    if (i < d && col < dv) st[static_cast<size_t>(i) * dv + col] = S[m];
+  }
+}
+
+// acc[TM][TN] += sum over k < K of At[k][row0 + a] * B[k][col0 + b]; At and B in shared memory, k-major
+template <int TM, int TN>
+__device__ __forceinline__ void tile_product(const float* At, int lda, const float* B, int ldb, int K, int row0,
+                                             int col0, float (&acc)[TM][TN]) {
+  for (int k = 0; k < K; ++k) {
+    float a[TM], b[TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i) a[i] = At[k * lda + row0 + i];
+#pragma unroll
+    for (int j = 0; j < TN; ++j) b[j] = B[k * ldb + col0 + j];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+  }
+}
+
+constexpr int RC_LD = RC + 4;        // row stride of the k-major tiles [e][token]
+constexpr int RV_LD = RD + 4;        // row stride of V and of a slab of S_before [k][column]
+constexpr size_t kChunkSmemFloats = 2 * RD * RC_LD + RC * RC_LD + RC * RV_LD + RC + 1;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+retention_chunk_kernel(const T* __restrict__ x, int in_stride, const float* __restrict__ qf,
+                       const float* __restrict__ kf, const float* __restrict__ before, float* __restrict__ o,
+                       const float* __restrict__ decay, const int* __restrict__ cu_q,
+                       const int* __restrict__ chunk_base, int num_rows, int heads, int d, int dv) {
+  extern __shared__ float smem[];
+  float* qt = smem;                          // [d][RC_LD]: q, k-major
+  float* kt = qt + RD * RC_LD;               // [d][RC_LD]: k; later a slab of S_before [RC][RV_LD]... kept apart:
+  float* at = kt + RD * RC_LD;               // [RC][RC_LD]: A transposed, at[j][i] = decay^(i-j) q_i . k_j (j <= i)
+  float* vb = at + RC * RC_LD;               // [RC][RV_LD]: V, then slabs of S_before
+  float* pw = vb + RC * RV_LD;               // decay^0 .. decay^RC
+
+  const int slot = blockIdx.x, h = blockIdx.y;
+  if (slot >= chunk_base[num_rows]) return;
+  int r = 0;
+  while (chunk_base[r + 1] <= slot) ++r;     // the row of this chunk (a handful of rows)
+  const int first = cu_q[r], n = cu_q[r + 1] - first;
+  const int base = (slot - chunk_base[r]) * RC;
+  const int L = min(RC, n - base);
+  const int t0 = first + base;
+  const float g = decay[h];
+  const int hd = heads * d;
+  const int voff = 2 * heads * d + h * dv;
+
+  for (int idx = threadIdx.x; idx < d * RC; idx += blockDim.x) {
+    const int i = idx / d, e = idx - i * d;                     // consecutive threads read consecutive e
+    const bool ok = i < L;
+    qt[e * RC_LD + i] = ok ? qf[static_cast<size_t>(t0 + i) * hd + h * d + e] : 0.0f;
+    kt[e * RC_LD + i] = ok ? kf[static_cast<size_t>(t0 + i) * hd + h * d + e] : 0.0f;
+  }
+  for (int idx = threadIdx.x; idx < RC * dv; idx += blockDim.x) {
+    const int j = idx / dv, col = idx - j * dv;
+    vb[j * RV_LD + col] = j < L ? to_f32<T>(x[static_cast<size_t>(t0 + j) * in_stride + voff + col]) : 0.0f;
+  }
+  if (threadIdx.x <= RC) pw[threadIdx.x] = threadIdx.x == 0 ? 1.0f : exp2f(static_cast<float>(threadIdx.x) * log2f(g));
+  __syncthreads();
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;      // 16 x 16 threads
+  {
+    // A[i][j] for i in 4 ty .., j in 4 tx ..
+    float acc[4][4] = {};
+    tile_product<4, 4>(qt, RC_LD, kt, RC_LD, d, ty * 4, tx * 4, acc);
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int i = ty * 4 + a, j = tx * 4 + b;
+        at[j * RC_LD + i] = j <= i ? acc[a][b] * pw[i - j] : 0.0f;
+      }
+  }
+  __syncthreads();
+  // o[i][col] for i in 4 ty .., col in 8 tx ..: A V first, then decay^(i+1) q_i^T S_before in slabs of RC rows of S
+  float out[4][8] = {};
+  tile_product<4, 8>(at, RC_LD, vb, RV_LD, RC, ty * 4, tx * 8, out);
+  float inter[4][8] = {};
+  const float* sb = before + (static_cast<size_t>(slot) * heads + h) * d * dv;
+  for (int e0 = 0; e0 < d; e0 += RC) {
+    __syncthreads();                                            // vb is free
+    const int rows = min(RC, d - e0);
+    for (int idx = threadIdx.x; idx < rows * dv; idx += blockDim.x) {
+      const int e = idx / dv, col = idx - e * dv;
+      vb[e * RV_LD + col] = sb[static_cast<size_t>(e0 + e) * dv + col];
+    }
+    __syncthreads();
+    tile_product<4, 8>(qt + e0 * RC_LD, RC_LD, vb, RV_LD, rows, ty * 4, tx * 8, inter);
+  }
+#pragma unroll
+  for (int a = 0; a < 4; ++a) {
+    const int i = ty * 4 + a;
+    if (i >= L) continue;
+    const float w = pw[i] * g;                                  // decay^(i+1)
+    float* dst = o + (static_cast<size_t>(t0 + i) * heads + h) * dv;
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      const int col = tx * 8 + b;
+      if (col < dv) dst[col] = fmaf(w, inter[a][b], out[a][b]);
+    }
+  }
+}
+
+template <typename T>
+static int launch_chunked(const void* x, int in_stride, float* o, float* state, const float* decay,
+                          const float* inv_freq, int rot_dim, float k_scale, const int* positions, const int* cu_q,
+                          const int* prefix_len, const int* state_slots, int num_rows, int heads, int d, int dv,
+                          int tokens, int max_chunks, float* qf, float* kf, float* before, int* chunk_base,
+                          cudaStream_t stream) {
+  const T* xt = static_cast<const T*>(x);
+  retention_rotate_kernel<T><<<dim3(tokens, (2 * heads * d + 255) / 256), 256, 0, stream>>>(
+      xt, in_stride, qf, kf, inv_freq, rot_dim, k_scale, positions, heads, d);
+  retention_chunk_base_kernel<<<1, 32, 0, stream>>>(cu_q, num_rows, chunk_base);
+  const dim3 sgrid(num_rows, heads, ((d + 31) / 32) * ((dv + 31) / 32));
+  retention_state_kernel<T><<<sgrid, 256, 0, stream>>>(xt, in_stride, kf, before, state, decay, cu_q, prefix_len,
+                                                       state_slots, chunk_base, heads, d, dv);
+  const size_t smem = kChunkSmemFloats * sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(retention_chunk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  retention_chunk_kernel<T><<<dim3(max_chunks, heads), 256, smem, stream>>>(xt, in_stride, qf, kf, before, o, decay, cu_q,
+                                                                             chunk_base, num_rows, heads, d, dv);
+  return b200_check_launch();
+}
+
+// The same result as b200_retention for steps with long rows.  `max_chunks` bounds the step's chunks of 64 tokens
+// (sum over rows of ceil(tokens of the row / 64)); scratch: qf, kf [tokens, heads * d] floats, before
+// [max_chunks, heads, d, dv] floats, chunk_base [num_rows + 1] ints.  Heads up to 128 wide.
+B200_EXPORT int b200_retention_chunked(const void* x, int dtype, int in_stride, float* o, float* state,
+                                       const float* decay, const float* inv_freq, int rot_dim, float k_scale,
+                                       const int* positions, const int* cu_q, const int* prefix_len,
+                                       const int* state_slots, int num_rows, int heads, int d, int dv, int tokens,
+                                       int max_chunks, float* qf, float* kf, float* before, int* chunk_base,
+                                       cudaStream_t stream) {
+  if (num_rows <= 0 || tokens <= 0) return 0;
+  if (heads <= 0 || heads > 65535 || d <= 0 || d > RD || dv <= 0 || dv > RD || rot_dim < 0 || rot_dim > d ||
+      (rot_dim & 1) || max_chunks <= 0)
+    return B200_BAD_SIZE;
+  if (dtype == B200_F32)
+    return launch_chunked<float>(x, in_stride, o, state, decay, inv_freq, rot_dim, k_scale, positions, cu_q,
+                                 prefix_len, state_slots, num_rows, heads, d, dv, tokens, max_chunks, qf, kf, before,
+                                 chunk_base, stream);
+  if (dtype == B200_BF16)
+    return launch_chunked<__nv_bfloat16>(x, in_stride, o, state, decay, inv_freq, rot_dim, k_scale, positions, cu_q,
+                                         prefix_len, state_slots, num_rows, heads, d, dv, tokens, max_chunks, qf, kf,
+                                         before, chunk_base, stream);
+  return B200_BAD_DTYPE;
+}
+
 B200_EXPORT int b200_retention(const void* x, int dtype, int in_stride, float* o, float* state, const float* decay,
                                const float* inv_freq, int rot_dim, float k_scale, const int* positions,
                                const int* cu_q, const int* prefix_len, const int* state_slots, int num_rows, int heads,

@@ -290,11 +290,15 @@ def tcgen05_attention_launches() -> tuple:
 
 def prefill_attention(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefix_len, rows, n_rows,
                       max_q_len, num_heads, num_kv_heads, head_dim, page_size, window, scale,
-                      tiles_per_cta: int = 0, v_head_dim: Optional[int] = None, softcap: float = 0.0) -> None:
+                      tiles_per_cta: int = 0, v_head_dim: Optional[int] = None, softcap: float = 0.0,
+                      precise_weights: bool = False) -> None:
     """Causal attention of prompt portions over the paged cache (rows: which batch rows).
 
     ``v_head_dim``: the width of a value (and of an output) vector where it differs from a key's;
-    ``softcap`` > 0: a score becomes cap * tanh(score / cap) before the mask.  Both take the all-sizes kernel.
+    ``softcap`` > 0: a score becomes cap * tanh(score / cap) before the mask; ``precise_weights``: the softmax
+    weights enter the product with the values as two bfloat16 terms (about 16 bits) instead of one.  Values of
+    another width than keys take the all-sizes kernel, whose weights are floats; a soft-cap or precise weights take
+    the mma.sync kernel, not the tcgen05 one (whose weights are single bfloat16 numbers in tensor memory).
 
     ``tiles_per_cta`` (head size 128 on the tcgen05 kernel only): 1 or 2 tiles of 128 query vectors per
     CTA, 0 lets the kernel's launcher choose by the size of the grid."""
@@ -305,13 +309,13 @@ def prefill_attention(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefi
     if k_cache.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelError("q, cache and output must share a dtype")
     dv = int(v_head_dim or head_dim)
-    plain = dv == head_dim and not softcap > 0.0
-    if plain and decode_uses_tensor_cores(q.dtype, num_heads, num_kv_heads, head_dim, page_size):
+    cap = float(softcap or 0.0)
+    if dv == head_dim and decode_uses_tensor_cores(q.dtype, num_heads, num_kv_heads, head_dim, page_size):
         if k_cache.shape[1] != num_kv_heads or k_cache.shape[2] != page_size:
             raise KernelError("the cache must be [pages + 1, kv_heads, page_size, head_dim]")
         box_rows = min(page_size, 32)
         group = num_heads // num_kv_heads
-        if head_dim == 128 and 128 % group == 0 and max_q_len * group >= 128:
+        if head_dim == 128 and 128 % group == 0 and max_q_len * group >= 128 and not cap > 0.0 and not precise_weights:
             # head size 128 and at least one full tile of 128 query vectors: the tcgen05 kernel
             rc = load_cuda_library("attention_tcgen05.cu").b200_prefill_attention_tcgen05(
                 _p(q), kv_tensor_map(k_cache, box_rows), kv_tensor_map(v_cache, box_rows), _p(out), _p(block_table),
@@ -323,13 +327,14 @@ def prefill_attention(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefi
         rc = _attention_mma(head_dim).b200_prefill_attention_mma(
             _p(q), kv_tensor_map(k_cache, box_rows), kv_tensor_map(v_cache, box_rows), _p(out), _p(block_table),
             block_table.shape[-1], _p(cu_q), _p(kv_len), _p(prefix_len), _p(rows), n_rows, max_q_len, num_heads,
-            num_kv_heads, page_size, int(window or 0), ctypes.c_float(scale), _p(error_word(q.device)), _stream())
+            num_kv_heads, page_size, int(window or 0), ctypes.c_float(scale), ctypes.c_float(cap),
+            int(bool(precise_weights)), _p(error_word(q.device)), _stream())
         _ok(rc, "prefill_attention_mma")
         return
     rc = _attention(max(head_dim, dv)).b200_prefill_attention(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(block_table), block_table.shape[-1], _p(cu_q),
         _p(kv_len), _p(prefix_len), _p(rows), n_rows, max_q_len, num_heads, num_kv_heads, page_size,
-        int(window or 0), ctypes.c_float(scale), _code(q), head_dim, dv, ctypes.c_float(softcap or 0.0), _stream())
+        int(window or 0), ctypes.c_float(scale), _code(q), head_dim, dv, ctypes.c_float(cap), _stream())
     _ok(rc, "prefill_attention")
 
 
@@ -373,8 +378,8 @@ def kv_tensor_map(cache: torch.Tensor, box_rows: int):
 
 def decode_ctas_per_split(dtype: torch.dtype, n_rows: int, num_heads: int, num_kv_heads: int, head_dim: int,
                           page_size: int, plain: bool = True) -> int:
-    """CTAs that the decode kernel launches for each split of the keys (``plain``: values as wide as keys and
-    no soft-cap, the case the tensor-core kernel takes)."""
+    """CTAs that the decode kernel launches for each split of the keys (``plain``: values as wide as keys, the
+    case the tensor-core kernel takes)."""
     if plain and decode_uses_tensor_cores(dtype, num_heads, num_kv_heads, head_dim, page_size):
         return n_rows * num_kv_heads
     return n_rows * num_kv_heads * ((num_heads // num_kv_heads + 3) // 4)
@@ -387,9 +392,9 @@ def decode_scratch_floats(n_rows: int, num_heads: int, head_dim: int, splits: in
 
 def decode_attention(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_len, rows, n_rows,
                      num_heads, num_kv_heads, head_dim, page_size, window, scale, splits,
-                     v_head_dim: Optional[int] = None, softcap: float = 0.0) -> None:
+                     v_head_dim: Optional[int] = None, softcap: float = 0.0, precise_weights: bool = False) -> None:
     """Attention of single decoded tokens, the keys split over ``splits`` blocks per row (``v_head_dim``,
-    ``softcap``: see ``prefill_attention``)."""
+    ``softcap``, ``precise_weights``: see ``prefill_attention``)."""
     _cuda(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_len, rows)
     _contig(q, k_cache, v_cache, out, block_table, scratch)
     if n_rows == 0:
@@ -397,7 +402,7 @@ def decode_attention(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_le
     if k_cache.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelError("q, cache and output must share a dtype")
     dv = int(v_head_dim or head_dim)
-    plain = dv == head_dim and not softcap > 0.0
+    plain = dv == head_dim
     need = decode_scratch_floats(n_rows, num_heads, max(head_dim, dv), splits)
     if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
         raise KernelError(f"decode attention needs {need} floats of scratch")
@@ -408,7 +413,8 @@ def decode_attention(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_le
         rc = _attention_mma(head_dim).b200_decode_attention_mma(
             _p(q), kv_tensor_map(k_cache, box_rows), kv_tensor_map(v_cache, box_rows), _p(out), _p(scratch), _p(block_table), block_table.shape[-1],
             _p(cu_q), _p(kv_len), _p(rows), n_rows, num_heads, num_kv_heads, page_size, int(window or 0),
-            ctypes.c_float(scale), splits, _p(error_word(q.device)), _stream())
+            ctypes.c_float(scale), splits, ctypes.c_float(softcap or 0.0), int(bool(precise_weights)),
+            _p(error_word(q.device)), _stream())
         in_kernel = splits == 1 or (splits in (2, 4, 8) and splits * num_kv_heads * n_rows <= _sm_count(q.device))
         _ok(rc, "decode_attention_mma", 1 if in_kernel else 2)      # (a cluster of 2, 4 or 8 splits combines them itself)
         return
@@ -1346,11 +1352,17 @@ def conv_qkv_post(x: torch.Tensor, conv_weight: Optional[torch.Tensor], state: O
     _ok(rc, "conv_qkv_post")
 
 
+RETENTION_CHUNKED_FROM = 32        # a step whose longest row has this many tokens takes the chunked kernels
+
+
 def retention(x: torch.Tensor, state: torch.Tensor, decay: torch.Tensor, inv_freq: Optional[torch.Tensor],
-              rot_dim: int, k_scale: float, ctx, heads: int, head_dim: int, v_head_dim: int) -> torch.Tensor:
+              rot_dim: int, k_scale: float, ctx, heads: int, head_dim: int, v_head_dim: int,
+              chunked: Optional[bool] = None) -> torch.Tensor:
     """o [tokens, heads * v_head_dim] (float32) of S_t = decay S_(t-1) + k_t v_t^T, o_t = S_t^T q_t over the step's
     rows; q, k (rotated by position * inv_freq, k then times ``k_scale``) and v are the first columns of ``x``;
-    ``state`` [slots + 1, heads, head_dim, v_head_dim] float32 is read (rows with a prefix) and written."""
+    ``state`` [slots + 1, heads, head_dim, v_head_dim] float32 is read (rows with a prefix) and written.
+    Two forms with the same result up to rounding: a scan that runs the recurrence token by token (steps of short
+    rows), and, for steps with long rows and heads up to 128 wide, chunks of 64 tokens (``chunked`` forces one)."""
     _cuda(x, state, decay, inv_freq)
     _contig(x, state, decay, inv_freq)
     _f32(state, decay, inv_freq)
@@ -1358,7 +1370,23 @@ def retention(x: torch.Tensor, state: torch.Tensor, decay: torch.Tensor, inv_fre
             or decay.numel() != heads:
         raise KernelError("retention: sizes of the projection, the state or the decays do not fit")
     o = torch.empty((x.shape[0], heads * v_head_dim), dtype=torch.float32, device=x.device)
-    rc = load_cuda_library("retention.cu").b200_retention(
+    lib = load_cuda_library("retention.cu")
+    tokens = x.shape[0]
+    longest = int(getattr(ctx, "max_q_len", 0) or tokens)
+    if (chunked if chunked is not None else longest >= RETENTION_CHUNKED_FROM) and head_dim <= 128 and v_head_dim <= 128:
+        # long rows: the state is carried chunk by chunk and every chunk's outputs are computed on their own
+        max_chunks = tokens // 64 + ctx.num_rows
+        qf = torch.empty((2, tokens, heads * head_dim), dtype=torch.float32, device=x.device)
+        before = torch.empty((max_chunks, heads, head_dim, v_head_dim), dtype=torch.float32, device=x.device)
+        chunk_base = torch.empty(ctx.num_rows + 1, dtype=torch.int32, device=x.device)
+        rc = lib.b200_retention_chunked(
+            _p(x), _code(x), x.shape[1], _p(o), _p(state), _p(decay), _p(inv_freq),
+            int(rot_dim if inv_freq is not None else 0), ctypes.c_float(k_scale), _p(ctx.positions), _p(ctx.cu_q),
+            _p(ctx.prefix_len), _p(ctx.state_slots), ctx.num_rows, heads, head_dim, v_head_dim, tokens, max_chunks,
+            _p(qf[0]), _p(qf[1]), _p(before), _p(chunk_base), _stream())
+        _ok(rc, "retention_chunked", 4)
+        return o
+    rc = lib.b200_retention(
         _p(x), _code(x), x.shape[1], _p(o), _p(state), _p(decay), _p(inv_freq),
         int(rot_dim if inv_freq is not None else 0), ctypes.c_float(k_scale), _p(ctx.positions), _p(ctx.cu_q),
         _p(ctx.prefix_len), _p(ctx.state_slots), ctx.num_rows, heads, head_dim, v_head_dim, _stream())

@@ -138,7 +138,8 @@ class GatedConvAttention(Part):
       * ``position_encoding``: half-split rotation of q and k;
       * ``v_mix`` "source": this layer's v is kept for the step under the name ``v_mix_group``; "mix": v becomes
         (1 - vmix) v + vmix v_source, and that is what the cache holds;
-      * ``softcap``: score <- cap * tanh(score / cap) after ``softmax_scale``;
+      * ``softcap``: score <- cap * tanh(score / cap) after ``softmax_scale``; the softmax weights stay floats
+        (all-sizes kernel) or enter the product with the values as two bfloat16 terms (tensor-core kernel);
       * ``window``: only the last W keys are read;
       * ``gate``: the heads' outputs are multiplied by sigmoid(g) before the output projection.
     No bias."""
@@ -225,17 +226,18 @@ class GatedConvAttention(Part):
             ops.prefill_attention(q, cache.k, cache.v, out, ctx.block_tables[g], ctx.cu_q, ctx.kv_len,
                                   ctx.prefix_len, ctx.prefill_rows, ctx.num_prefill, ctx.max_q_len,
                                   self.nh, self.nkv, self.d, page, self.window, self.scale,
-                                  v_head_dim=self.dv, softcap=self.softcap)
+                                  v_head_dim=self.dv, softcap=self.softcap, precise_weights=True)
         if ctx.num_decode:
             bound = min(ctx.kv_len_bound, self.window) if self.window else ctx.kv_len_bound
-            plain = self.dv == self.d and not self.softcap > 0.0
+            plain = self.dv == self.d
             per_split = ops.decode_ctas_per_split(q.dtype, ctx.num_decode, self.nh, self.nkv, self.d, page, plain)
             splits = decode_splits(per_split, bound, ctx.sm_count)
             need = ops.decode_scratch_floats(ctx.num_decode, self.nh, max(self.d, self.dv), splits)
             scratch = ctx.scratch(need) if need else None
             ops.decode_attention(q, cache.k, cache.v, out, scratch, ctx.block_tables[g], ctx.cu_q,
                                  ctx.kv_len, ctx.decode_rows, ctx.num_decode, self.nh, self.nkv, self.d,
-                                 page, self.window, self.scale, splits, v_head_dim=self.dv, softcap=self.softcap)
+                                 page, self.window, self.scale, splits, v_head_dim=self.dv, softcap=self.softcap,
+                                 precise_weights=True)
         if self.gate:
             ops.sigmoid_gate_mul(out, packed, self.qkv_channels)
         return ops.linear(out, p["o_proj"])

@@ -11,7 +11,6 @@ tensor names to tensors; ``config`` is the dict of a config.json.
 """
 from __future__ import annotations
 
-import math
 from typing import Dict, List, Optional
 
 import torch
@@ -38,9 +37,9 @@ def causal_taps(u: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return y
 
 
-def canon(h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """What a sublayer reads: h + conv(h)."""
-    return h + causal_taps(h, w)
+def canon(h: torch.Tensor, w: Optional[torch.Tensor]) -> torch.Tensor:
+    """What a sublayer reads: h + conv(h) (h itself in a model without this convolution)."""
+    return h if w is None else h + causal_taps(h, w)
 
 
 def rotate_half_split(x: torch.Tensor, base: float, dims: int, factor: float = 1.0) -> torch.Tensor:
@@ -59,6 +58,19 @@ def rotate_half_split(x: torch.Tensor, base: float, dims: int, factor: float = 1
     return out
 
 
+def retention_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor,
+                         S0: Optional[torch.Tensor] = None, return_state: bool = False):
+    """S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t, token by token.  q, k [T, H, d]; v [T, H, dv]."""
+    T, H, d = q.shape
+    dv = v.shape[-1]
+    S = torch.zeros(H, d, dv, dtype=q.dtype) if S0 is None else S0.clone()
+    o = torch.zeros(T, H, dv, dtype=q.dtype)
+    for t in range(T):
+        S = decay[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
+        o[t] = torch.einsum("hdv,hd->hv", S, q[t])
+    return (o, S) if return_state else o
+
+
 def retention_mixer(h: torch.Tensor, W: Dict[str, torch.Tensor], m: dict, eps: float) -> torch.Tensor:
     """Linear attention with a fixed decay per head, no softmax and no denominator."""
     T = h.shape[0]
@@ -72,15 +84,28 @@ def retention_mixer(h: torch.Tensor, W: Dict[str, torch.Tensor], m: dict, eps: f
         q = rotate_half_split(q, rot["base"], rot["dims"], factor)
         k = rotate_half_split(k, rot["base"], rot["dims"], factor)
     k = k * d ** -0.5
-    decay = torch.tensor(m["decay"], dtype=h.dtype)
-    S = torch.zeros(H, d, dv, dtype=h.dtype)
-    o = torch.zeros(T, H, dv, dtype=h.dtype)
-    for t in range(T):
-        S = decay[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
-        o[t] = torch.einsum("hdv,hd->hv", S, q[t])
+    o = retention_recurrence(q, k, v, torch.tensor(m["decay"], dtype=h.dtype))
     o = unit_rms(o, eps).reshape(T, H * dv)
     gate = h @ W["g"].T
     return (o * (gate * torch.sigmoid(gate))) @ W["o"].T
+
+
+def capped_causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
+                            cap: Optional[float]) -> torch.Tensor:
+    """softmax over j <= i of cap * tanh(scale q_i . k_j / cap) (no cap: the scaled score itself), times v.
+    q [T, H, d], k [T, G, d], v [T, G, dv]; query head h reads key/value head h // (H / G)."""
+    T, H, _ = q.shape
+    G = k.shape[1]
+    out = torch.zeros(T, H, v.shape[-1], dtype=q.dtype)
+    mask = torch.tril(torch.ones(T, T, dtype=torch.bool))
+    for head in range(H):
+        kv = head // (H // G)
+        s = (q[:, head] @ k[:, kv].T) * scale
+        if cap:
+            s = cap * torch.tanh(s / cap)
+        s = s.masked_fill(~mask, float("-inf"))
+        out[:, head] = torch.softmax(s, dim=-1) @ v[:, kv]
+    return out
 
 
 def attention_mixer(h: torch.Tensor, W: Dict[str, torch.Tensor], m: dict, v_first: Optional[torch.Tensor],
@@ -102,17 +127,7 @@ def attention_mixer(h: torch.Tensor, W: Dict[str, torch.Tensor], m: dict, v_firs
         lam = W["vmix"]
         v = (1.0 - lam) * v + lam * v_first
     v_out = v
-    v = v.view(T, G, dv)
-    out = torch.zeros(T, H, dv, dtype=h.dtype)
-    cap = m.get("softcap")
-    mask = torch.tril(torch.ones(T, T, dtype=torch.bool))
-    for head in range(H):
-        kv = head // (H // G)
-        s = (q[:, head] @ k[:, kv].T) * m["scale"]
-        if cap:
-            s = cap * torch.tanh(s / cap)
-        s = s.masked_fill(~mask, float("-inf"))
-        out[:, head] = torch.softmax(s, dim=-1) @ v[:, kv]
+    out = capped_causal_attention(q, k, v.view(T, G, dv), m["scale"], m.get("softcap"))
     gate = torch.sigmoid(h @ W["g"].T)
     return (out.reshape(T, H * dv) * gate) @ W["o"].T, v_out
 
@@ -140,7 +155,9 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens: List[int], d
     for i, layer in enumerate(config["layers"]):
         p = f"l{i}."
         m = layer["mixer"]
-        h = canon(scalar_rms_norm(x, weights[p + "norm1"].to(dtype), eps), weights[p + "canon1"].to(dtype))
+        taps = {n: weights[p + n].to(dtype) if config.get("canon") else None for n in ("canon1", "canon2")
+                if config.get("canon") is None or p + n in weights}
+        h = canon(scalar_rms_norm(x, weights[p + "norm1"].to(dtype), eps), taps["canon1"])
         W = sub(weights, p + "mix.", dtype)
         if layer["type"] == "retention":
             y = retention_mixer(h, W, m, eps)
@@ -153,7 +170,7 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens: List[int], d
             raise ValueError(layer["type"])
         x = x + y
         if layer.get("mlp") is not None:
-            h = canon(scalar_rms_norm(x, weights[p + "norm2"].to(dtype), eps), weights[p + "canon2"].to(dtype))
+            h = canon(scalar_rms_norm(x, weights[p + "norm2"].to(dtype), eps), taps["canon2"])
             x = x + dense_ff(h, sub(weights, p + "mlp.", dtype), eps)
         if layer_outputs is not None:
             layer_outputs.append(x.clone())
