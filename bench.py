@@ -390,7 +390,8 @@ def kernel_table(size, peak):
         return types.SimpleNamespace(
             num_rows=R, row_of_token=i32(row_of), cu_q=i32(cu), positions=i32(pos), prefix_len=i32([p for p, _ in rows]),
             kv_len=i32([p + n for p, n in rows]), state_slots=i32(list(range(1, R + 1))), slots=i32(slots), table=table,
-            rows=i32(list(range(R))), tokens=cu[-1], pages=R * width + 1)
+            rows=i32(list(range(R))), tokens=cu[-1], pages=R * width + 1, max_q_len=max(n for _, n in rows),
+            num_prefill=sum(n > 1 for _, n in rows))
 
     for phase, c in (("prefill", step([(0, ctx_len)])), ("decode", step([(ctx_len - 1, 1)] * rows_dec))):
         T = c.tokens
@@ -417,10 +418,9 @@ def kernel_table(size, peak):
         qstate = torch.zeros(rows_dec + 1, 2, cq, device=dev)
         inv_freq = torch.pow(torch.tensor(1e6), -torch.arange(0, d, 2) / d).to(dev)
         vfirst, lam = torch.randn(T, nkv * d, device=dev), torch.full((1,), 0.5, device=dev)
-        put(f"{phase}.kefetar.conv_qkv_post", timed_alone(lambda: (
-            ops.conv_qkv_post(packed, qw, qstate, c, q, k_cache, v_cache, inv_freq, d, c.slots, nh, nkv, d, d,
-                              vmix=lam, v_first=vfirst, v_mode=2),
-            ops.taps_state_update(packed, 3, cq, qstate, c)), flush), T * cq * 4 + T * nkv * d * 4)
+        put(f"{phase}.kefetar.conv_qkv_post", timed_alone(lambda: ops.conv_qkv_post(
+            packed, qw, qstate, c, q, k_cache, v_cache, inv_freq, d, c.slots, nh, nkv, d, d, vmix=lam, v_first=vfirst,
+            v_mode=2), flush), T * cq * 4 + T * nkv * d * 4)
         qkv = packed[:, :cq].contiguous()
         cos, sin = torch.ones(4096, d // 2, device=dev), torch.zeros(4096, d // 2, device=dev)
         hn = torch.ones(d, dtype=bf, device=dev)

@@ -1,7 +1,8 @@
 // Between the packed q/k/v projection and attention, for a mixer whose q, k and v pass through a short causal
 // convolution over time: the convolution (inputs before the step come from the request's state, token_conv.cuh),
 // the half-split rotation of q and k by angles computed from the position, an optional mix of v with the v of an
-// earlier layer, and the stores: q to its buffer, k and v (as they will be attended) into the paged cache.
+// earlier layer, and the stores: q to its buffer, k and v (as they will be attended) into the paged cache; then the
+// rows' convolution states are brought up to date (as in token_conv.cu).
 //
 //   u = conv(projection)                                     (no convolution: u = projection)
 //   rotation of the first rot_dim coordinates of a head:  (a, b) = (u[i], u[i + rot_dim/2]),
@@ -72,48 +73,6 @@ conv_qkv_post_kernel(TapsInput<T> in, T* __restrict__ q_out, T* __restrict__ k_c
 // every channel passes the convolution once and every pair takes one sine and cosine.  A head has
 // rot_dim / 16 paired items and (d - rot_dim) / 8 single ones; v has dv / 8 single items per head.
 template <typename T>
-__device__ __forceinline__ void store8(T* p, const float* v) {
-  if constexpr (sizeof(T) == 4) {
-    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
-    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
-  } else {
-    uint4 u;
-    __nv_bfloat162 h;
-    h = __floats2bfloat162_rn(v[0], v[1]); u.x = *reinterpret_cast<uint32_t*>(&h);
-    h = __floats2bfloat162_rn(v[2], v[3]); u.y = *reinterpret_cast<uint32_t*>(&h);
-    h = __floats2bfloat162_rn(v[4], v[5]); u.z = *reinterpret_cast<uint32_t*>(&h);
-    h = __floats2bfloat162_rn(v[6], v[7]); u.w = *reinterpret_cast<uint32_t*>(&h);
-    *reinterpret_cast<uint4*>(p) = u;
-  }
-}
-
-// y[0..8) = the convolution's outputs of channels c .. c + 7 of token t
-template <typename T>
-__device__ __forceinline__ void taps_value8(const TapsInput<T>& in, const TapsRow& row, int t, int c, float* y) {
-  float u[8];
-  load_floats<T, 8>(in.x + static_cast<size_t>(t) * in.in_stride + c, u);
-  if (in.w == nullptr) {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) y[i] = u[i];
-    return;
-  }
-  const int taps = in.taps;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) y[i] = in.w[static_cast<size_t>(c + i) * taps + taps - 1] * u[i];
-  for (int back = 1; back < taps; ++back) {
-    if (back <= row.local) {
-      load_floats<T, 8>(in.x + static_cast<size_t>(t - back) * in.in_stride + c, u);
-    } else if (row.has_past) {
-      load_floats<float, 8>(row.state + static_cast<size_t>(taps - 1 - (back - row.local)) * in.channels + c, u);
-    } else {
-      continue;
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) y[i] = fmaf(in.w[static_cast<size_t>(c + i) * taps + taps - 1 - back], u[i], y[i]);
-  }
-}
-
-template <typename T>
 __global__ void __launch_bounds__(128)
 conv_qkv_post_vec_kernel(TapsInput<T> in, T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
                          const float* __restrict__ inv_freq, int rot_dim, const int* __restrict__ positions,
@@ -127,6 +86,7 @@ conv_qkv_post_vec_kernel(TapsInput<T> in, T* __restrict__ q_out, T* __restrict__
   const int qk_items = (nh + nkv) * per_head;
   if (item >= qk_items + nkv * (dv / 8)) return;
   const TapsRow row = taps_row(in, t);
+  const bool own = taps_single(in, t);
   const int cq = nh * d, ck = nkv * d;
   int slot = -1, page = 0, off = 0;
   if (slots != nullptr) {
@@ -145,9 +105,9 @@ conv_qkv_post_vec_kernel(TapsInput<T> in, T* __restrict__ q_out, T* __restrict__
     const bool paired = part < half / 8;
     const int e = paired ? part * 8 : rot_dim + (part - half / 8) * 8;
     const int c = head * d + e;                                               // (q and k channels are contiguous)
-    taps_value8(in, row, t, c, a);
+    taps_value8(in, row, t, c, false, own, a);
     if (paired) {
-      taps_value8(in, row, t, c + half, b);
+      taps_value8(in, row, t, c + half, false, own, b);
       const float pos = static_cast<float>(positions[t]);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -170,7 +130,7 @@ conv_qkv_post_vec_kernel(TapsInput<T> in, T* __restrict__ q_out, T* __restrict__
   }
   const int vi = item - qk_items;
   const int kvh = vi / (dv / 8), e = (vi - kvh * (dv / 8)) * 8;
-  taps_value8(in, row, t, cq + ck + kvh * dv + e, a);
+  taps_value8(in, row, t, cq + ck + kvh * dv + e, false, own, a);
   float* vf = v_first + static_cast<size_t>(t) * (nkv * dv) + kvh * dv + e;
   if (v_mode == 1) {
     *reinterpret_cast<float4*>(vf) = make_float4(a[0], a[1], a[2], a[3]);
@@ -190,7 +150,7 @@ static int launch(const void* x, int in_stride, const float* w, int taps, float*
                   const int* cu_q, const int* prefix_len, const int* state_slots, void* q_out, void* k_cache,
                   void* v_cache, const float* inv_freq, int rot_dim, const int* positions, const int* slots, int nh,
                   int nkv, int d, int dv, int page_size, long long cache_slots, const float* vmix, float* v_first,
-                  int v_mode, int tokens, int* err, cudaStream_t stream) {
+                  int v_mode, int tokens, int num_rows, int all_single, int* err, cudaStream_t stream) {
   TapsInput<T> in;
   in.x = static_cast<const T*>(x); in.in_stride = in_stride; in.scale = nullptr; in.w = w; in.taps = w ? taps : 1;
   in.channels = nh * d + nkv * d + nkv * dv; in.state = state; in.row_of_token = row_of_token; in.cu_q = cu_q;
@@ -206,12 +166,18 @@ static int launch(const void* x, int in_stride, const float* w, int taps, float*
                                                            static_cast<T*>(v_cache), inv_freq, rot_dim, positions, slots,
                                                            nh, nkv, d, dv, page_size, cache_slots, vmix, v_first, v_mode,
                                                            err);
+    int rc = b200_check_launch();
+    if (rc != 0 || in.taps <= 1 || all_single) return rc;
+    taps_state_update_kernel<T><<<dim3(num_rows, (in.channels + 255) / 256), 256, 0, stream>>>(in, num_rows, 1);
     return b200_check_launch();
   }
   const dim3 grid(tokens, (in.channels + 255) / 256);
   conv_qkv_post_kernel<T><<<grid, 256, 0, stream>>>(in, static_cast<T*>(q_out), static_cast<T*>(k_cache),
                                                     static_cast<T*>(v_cache), inv_freq, rot_dim, positions, slots, nh,
                                                     nkv, d, dv, page_size, cache_slots, vmix, v_first, v_mode, err);
+  int rc = b200_check_launch();
+  if (rc != 0 || in.taps <= 1) return rc;
+  taps_state_update_kernel<T><<<dim3(num_rows, (in.channels + 255) / 256), 256, 0, stream>>>(in, num_rows, 0);
   return b200_check_launch();
 }
 
@@ -221,7 +187,8 @@ B200_EXPORT int b200_conv_qkv_post(const void* x, int dtype, int in_stride, cons
                                    const int* state_slots, void* q_out, void* k_cache, void* v_cache,
                                    const float* inv_freq, int rot_dim, const int* positions, const int* slots, int nh,
                                    int nkv, int d, int dv, int page_size, long long cache_slots, const float* vmix,
-                                   float* v_first, int v_mode, int tokens, int* err, cudaStream_t stream) {
+                                   float* v_first, int v_mode, int tokens, int num_rows, int all_single, int* err,
+                                   cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (nh <= 0 || nkv <= 0 || d <= 0 || dv <= 0 || page_size <= 0 || rot_dim < 0 || rot_dim > d || (rot_dim & 1))
     return B200_BAD_SIZE;
@@ -231,10 +198,10 @@ B200_EXPORT int b200_conv_qkv_post(const void* x, int dtype, int in_stride, cons
   if (dtype == B200_F32)
     return launch<float>(x, in_stride, w, taps, state, row_of_token, cu_q, prefix_len, state_slots, q_out, k_cache,
                          v_cache, inv_freq, rot_dim, positions, slots, nh, nkv, d, dv, page_size, cache_slots, vmix,
-                         v_first, v_mode, tokens, err, stream);
+                         v_first, v_mode, tokens, num_rows, all_single, err, stream);
   if (dtype == B200_BF16)
     return launch<__nv_bfloat16>(x, in_stride, w, taps, state, row_of_token, cu_q, prefix_len, state_slots, q_out,
                                  k_cache, v_cache, inv_freq, rot_dim, positions, slots, nh, nkv, d, dv, page_size,
-                                 cache_slots, vmix, v_first, v_mode, tokens, err, stream);
+                                 cache_slots, vmix, v_first, v_mode, tokens, num_rows, all_single, err, stream);
   return B200_BAD_DTYPE;
 }

@@ -35,6 +35,72 @@ poly_norm_kernel(T* __restrict__ out, const T* __restrict__ z, const float* __re
   }
 }
 
+// The same for rows of whole 16-byte pieces: eight elements a thread and turn; a row of up to 8,192 elements
+// stays in registers between the sums and the result.
+template <typename T>
+__global__ void __launch_bounds__(256)
+poly_norm_vec_kernel(T* __restrict__ out, const T* __restrict__ z, const float* __restrict__ coef, float eps, int width) {
+  __shared__ float scratch[33];
+  constexpr int KEEP = 4;
+  const size_t base = static_cast<size_t>(blockIdx.x) * width;
+  float kept[KEEP][8];
+  float s2 = 0.0f, s4 = 0.0f, s6 = 0.0f;
+  int turn = 0;
+  for (int c = threadIdx.x * 8; c < width; c += blockDim.x * 8, ++turn) {
+    float v[8];
+    load_floats<T, 8>(z + base + c, v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float v2 = v[i] * v[i], v3 = v2 * v[i];
+      s2 += v2;
+      s4 = fmaf(v2, v2, s4);
+      s6 = fmaf(v3, v3, s6);
+    }
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k)
+      if (k == turn) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) kept[k][i] = v[i];
+      }
+  }
+  s2 = block_sum(s2, scratch);
+  s4 = block_sum(s4, scratch);
+  s6 = block_sum(s6, scratch);
+  const float n = static_cast<float>(width);
+  const float r1 = coef[0] / sqrtf(s2 / n + eps), r2 = coef[1] / sqrtf(s4 / n + eps), r3 = coef[2] / sqrtf(s6 / n + eps);
+  const float e = coef[3];
+  turn = 0;
+  for (int c = threadIdx.x * 8; c < width; c += blockDim.x * 8, ++turn) {
+    float v[8];
+    bool have = false;
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k)
+      if (k == turn) {
+        have = true;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = kept[k][i];
+      }
+    if (!have) load_floats<T, 8>(z + base + c, v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float v2 = v[i] * v[i];
+      v[i] = fmaf(r1, v[i], fmaf(r2, v2, fmaf(r3, v2 * v[i], e)));
+    }
+    if constexpr (sizeof(T) == 4) {
+      *reinterpret_cast<float4*>(out + base + c) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(out + base + c + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+      uint4 u;
+      __nv_bfloat162 h;
+      h = __floats2bfloat162_rn(v[0], v[1]); u.x = *reinterpret_cast<uint32_t*>(&h);
+      h = __floats2bfloat162_rn(v[2], v[3]); u.y = *reinterpret_cast<uint32_t*>(&h);
+      h = __floats2bfloat162_rn(v[4], v[5]); u.z = *reinterpret_cast<uint32_t*>(&h);
+      h = __floats2bfloat162_rn(v[6], v[7]); u.w = *reinterpret_cast<uint32_t*>(&h);
+      *reinterpret_cast<uint4*>(out + base + c) = u;
+    }
+  }
+}
+
 // one warp per (token, head)
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -72,6 +138,16 @@ B200_EXPORT int b200_poly_norm(void* out, const void* z, const float* coef, floa
                                int dtype, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (width <= 0) return B200_BAD_SIZE;
+  if (width % 8 == 0 && (reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(z)) % 16 == 0 &&
+      (dtype == B200_F32 || dtype == B200_BF16)) {
+    if (dtype == B200_F32)
+      poly_norm_vec_kernel<float><<<tokens, 256, 0, stream>>>(static_cast<float*>(out), static_cast<const float*>(z),
+                                                              coef, eps, width);
+    else
+      poly_norm_vec_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>(
+          static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(z), coef, eps, width);
+    return b200_check_launch();
+  }
   if (dtype == B200_F32)
     poly_norm_kernel<float><<<tokens, 256, 0, stream>>>(static_cast<float*>(out), static_cast<const float*>(z), coef,
                                                         eps, width);

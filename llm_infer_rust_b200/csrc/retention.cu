@@ -210,14 +210,27 @@ retention_state_kernel(const T* __restrict__ x, int in_stride, const float* __re
     const int i = ti * 32 + ty + 8 * m;
     S[m] = (has_past && i < d && col < dv) ? st[static_cast<size_t>(i) * dv + col] : 0.0f;
   }
+  // A thread stages k and v of tokens ty + 8 m (m < 8) of a chunk, element tx of the tile's 32: the next chunk's
+  // values are fetched into registers while the recurrence runs over the current chunk.
+  const bool k_ok = ti * 32 + tx < d, v_ok = col < dv;
+  const float* kcol = kf + static_cast<size_t>(h) * d + ti * 32 + tx;
+  const T* vcol = x + voff + col;
+  float kn[8], vn[8];
+  auto fetch = [&](int base) {
+    const int L = min(RC, n - base);
+#pragma unroll
+    for (int m = 0; m < 8; ++m) {
+      const int j = ty + 8 * m;
+      const size_t t = static_cast<size_t>(first + base + j);
+      kn[m] = (j < L && k_ok) ? kcol[t * heads * d] : 0.0f;
+      vn[m] = (j < L && v_ok) ? to_f32<T>(vcol[t * in_stride]) : 0.0f;
+    }
+  };
+  if (n > 0) fetch(0);
   for (int base = 0, c = chunk_base[r]; base < n; base += RC, ++c) {
     const int L = min(RC, n - base);
-    for (int idx = threadIdx.x; idx < L * 32; idx += blockDim.x) {
-      const int j = idx >> 5, e = idx & 31;
-      const int t = first + base + j;
-      ks[j][e] = ti * 32 + e < d ? kf[static_cast<size_t>(t) * heads * d + h * d + ti * 32 + e] : 0.0f;
-      vs[j][e] = tj * 32 + e < dv ? to_f32<T>(x[static_cast<size_t>(t) * in_stride + voff + tj * 32 + e]) : 0.0f;
-    }
+#pragma unroll
+    for (int m = 0; m < 8; ++m) { ks[ty + 8 * m][tx] = kn[m]; vs[ty + 8 * m][tx] = vn[m]; }
     float* dst = before + (static_cast<size_t>(c) * heads + h) * d * dv;
 #pragma unroll
     for (int m = 0; m < 4; ++m) {
@@ -225,6 +238,7 @@ retention_state_kernel(const T* __restrict__ x, int in_stride, const float* __re
       if (i < d && col < dv) dst[static_cast<size_t>(i) * dv + col] = S[m];
     }
     __syncthreads();
+    if (base + RC < n) fetch(base + RC);
     for (int j = 0; j < L; ++j) {
       const float v = vs[j][tx];
 #pragma unroll
@@ -239,16 +253,25 @@ retention_state_kernel(const T* __restrict__ x, int in_stride, const float* __re
   }
 }
 
-// acc[TM][TN] += sum over k < K of At[k][row0 + a] * B[k][col0 + b]; At and B in shared memory, k-major
+// acc[TM][TN] += sum over k < K of At[k][row0 + a] * B[k][col0 + b]; At and B in shared memory, k-major, with
+// row strides, row0 and col0 that are multiples of 4 floats (16-byte loads)
 template <int TM, int TN>
 __device__ __forceinline__ void tile_product(const float* At, int lda, const float* B, int ldb, int K, int row0,
                                              int col0, float (&acc)[TM][TN]) {
+  static_assert(TM % 4 == 0 && TN % 4 == 0, "whole 16-byte pieces");
+#pragma unroll 2
   for (int k = 0; k < K; ++k) {
     float a[TM], b[TN];
 #pragma unroll
-    for (int i = 0; i < TM; ++i) a[i] = At[k * lda + row0 + i];
+    for (int i = 0; i < TM; i += 4) {
+      const float4 v = *reinterpret_cast<const float4*>(At + k * lda + row0 + i);
+      a[i] = v.x; a[i + 1] = v.y; a[i + 2] = v.z; a[i + 3] = v.w;
+    }
 #pragma unroll
-    for (int j = 0; j < TN; ++j) b[j] = B[k * ldb + col0 + j];
+    for (int j = 0; j < TN; j += 4) {
+      const float4 v = *reinterpret_cast<const float4*>(B + k * ldb + col0 + j);
+      b[j] = v.x; b[j + 1] = v.y; b[j + 2] = v.z; b[j + 3] = v.w;
+    }
 #pragma unroll
     for (int i = 0; i < TM; ++i)
 #pragma unroll
@@ -256,22 +279,47 @@ __device__ __forceinline__ void tile_product(const float* At, int lda, const flo
   }
 }
 
+// The same with the TM x 8 results in two groups of four columns, col0 .. and 64 + col0 ..: the 16 threads of a
+// row then read 16 neighbouring 16-byte pieces of B (no two of a quarter-warp in one bank)
+template <int TM>
+__device__ __forceinline__ void tile_product_split(const float* At, int lda, const float* B, int ldb, int K, int row0,
+                                                   int col0, float (&acc)[TM][8]) {
+#pragma unroll 2
+  for (int k = 0; k < K; ++k) {
+    float a[TM], b[8];
+#pragma unroll
+    for (int i = 0; i < TM; i += 4) {
+      const float4 v = *reinterpret_cast<const float4*>(At + k * lda + row0 + i);
+      a[i] = v.x; a[i + 1] = v.y; a[i + 2] = v.z; a[i + 3] = v.w;
+    }
+    const float4 lo = *reinterpret_cast<const float4*>(B + k * ldb + col0);
+    const float4 hi = *reinterpret_cast<const float4*>(B + k * ldb + 64 + col0);
+    b[0] = lo.x; b[1] = lo.y; b[2] = lo.z; b[3] = lo.w; b[4] = hi.x; b[5] = hi.y; b[6] = hi.z; b[7] = hi.w;
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+  }
+}
+
 constexpr int RC_LD = RC + 4;        // row stride of the k-major tiles [e][token]
 constexpr int RV_LD = RD + 4;        // row stride of V and of a slab of S_before [k][column]
-constexpr size_t kChunkSmemFloats = 2 * RD * RC_LD + RC * RC_LD + RC * RV_LD + RC + 1;
+static_assert(RC * RV_LD <= RD * RC_LD, "V and the slabs of S_before take the place of K");
+constexpr size_t kChunkSmemFloats = 2 * RD * RC_LD + RC * RC_LD + RC + 1;      // 87 KB: two blocks an SM
 
+// d a multiple of 4 and dv a multiple of 8 (16-byte pieces of the float and of the bfloat16 rows).
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 retention_chunk_kernel(const T* __restrict__ x, int in_stride, const float* __restrict__ qf,
                        const float* __restrict__ kf, const float* __restrict__ before, float* __restrict__ o,
                        const float* __restrict__ decay, const int* __restrict__ cu_q,
                        const int* __restrict__ chunk_base, int num_rows, int heads, int d, int dv) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   float* qt = smem;                          // [d][RC_LD]: q, k-major
-  float* kt = qt + RD * RC_LD;               // [d][RC_LD]: k; later a slab of S_before [RC][RV_LD]... kept apart:
+  float* kt = qt + RD * RC_LD;               // [d][RC_LD]: k, k-major; once A is made: V, then slabs of S_before
   float* at = kt + RD * RC_LD;               // [RC][RC_LD]: A transposed, at[j][i] = decay^(i-j) q_i . k_j (j <= i)
-  float* vb = at + RC * RC_LD;               // [RC][RV_LD]: V, then slabs of S_before
-  float* pw = vb + RC * RV_LD;               // decay^0 .. decay^RC
+  float* pw = at + RC * RC_LD;               // decay^0 .. decay^RC
+  float* vb = kt;                            // [RC][RV_LD]
 
   const int slot = blockIdx.x, h = blockIdx.y;
   if (slot >= chunk_base[num_rows]) return;
@@ -285,19 +333,49 @@ retention_chunk_kernel(const T* __restrict__ x, int in_stride, const float* __re
   const int hd = heads * d;
   const int voff = 2 * heads * d + h * dv;
 
-  for (int idx = threadIdx.x; idx < d * RC; idx += blockDim.x) {
-    const int i = idx / d, e = idx - i * d;                     // consecutive threads read consecutive e
-    const bool ok = i < L;
-    qt[e * RC_LD + i] = ok ? qf[static_cast<size_t>(t0 + i) * hd + h * d + e] : 0.0f;
-    kt[e * RC_LD + i] = ok ? kf[static_cast<size_t>(t0 + i) * hd + h * d + e] : 0.0f;
-  }
-  for (int idx = threadIdx.x; idx < RC * dv; idx += blockDim.x) {
-    const int j = idx / dv, col = idx - j * dv;
-    vb[j * RV_LD + col] = j < L ? to_f32<T>(x[static_cast<size_t>(t0 + j) * in_stride + voff + col]) : 0.0f;
+  {
+    // q and k: a thread fetches 16-byte pieces (4 consecutive e of one token), four pieces in flight
+    const int pieces = d / 4, total = RC * pieces;
+    for (int idx0 = threadIdx.x; idx0 < total; idx0 += 4 * blockDim.x) {
+      float4 qv[4], kv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = idx0 + u * blockDim.x;
+        const int i = idx / pieces, e = (idx - i * pieces) * 4;
+        const bool ok = idx < total && i < L;
+        const size_t at_ = static_cast<size_t>(t0 + (ok ? i : 0)) * hd + h * d + e;
+        qv[u] = ok ? *reinterpret_cast<const float4*>(qf + at_) : make_float4(0.f, 0.f, 0.f, 0.f);
+        kv[u] = ok ? *reinterpret_cast<const float4*>(kf + at_) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = idx0 + u * blockDim.x;
+        if (idx >= total) continue;
+        const int i = idx / pieces, e = (idx - i * pieces) * 4;
+        qt[(e + 0) * RC_LD + i] = qv[u].x; qt[(e + 1) * RC_LD + i] = qv[u].y;
+        qt[(e + 2) * RC_LD + i] = qv[u].z; qt[(e + 3) * RC_LD + i] = qv[u].w;
+        kt[(e + 0) * RC_LD + i] = kv[u].x; kt[(e + 1) * RC_LD + i] = kv[u].y;
+        kt[(e + 2) * RC_LD + i] = kv[u].z; kt[(e + 3) * RC_LD + i] = kv[u].w;
+      }
+    }
   }
   if (threadIdx.x <= RC) pw[threadIdx.x] = threadIdx.x == 0 ? 1.0f : exp2f(static_cast<float>(threadIdx.x) * log2f(g));
   __syncthreads();
   const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;      // 16 x 16 threads
+  // V of this chunk: fetched into registers now (8 columns a piece), stored over K once A is made
+  const int vpieces = dv / 8, vtotal = RC * vpieces;
+  float vreg[4][8];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int idx = threadIdx.x + u * blockDim.x;
+    const int j = idx / vpieces, col = (idx - j * vpieces) * 8;
+    if (idx < vtotal && j < L) {
+      load_floats<T, 8>(x + static_cast<size_t>(t0 + j) * in_stride + voff + col, vreg[u]);
+    } else {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) vreg[u][q] = 0.0f;
+    }
+  }
   {
     // A[i][j] for i in 4 ty .., j in 4 tx ..
     float acc[4][4] = {};
@@ -310,21 +388,53 @@ retention_chunk_kernel(const T* __restrict__ x, int in_stride, const float* __re
         at[j * RC_LD + i] = j <= i ? acc[a][b] * pw[i - j] : 0.0f;
       }
   }
-  __syncthreads();
-  // o[i][col] for i in 4 ty .., col in 8 tx ..: A V first, then decay^(i+1) q_i^T S_before in slabs of RC rows of S
-  float out[4][8] = {};
-  tile_product<4, 8>(at, RC_LD, vb, RV_LD, RC, ty * 4, tx * 8, out);
-  float inter[4][8] = {};
+  __syncthreads();                                              // A is whole, K is free
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int idx = threadIdx.x + u * blockDim.x;
+    if (idx < vtotal) {
+      const int j = idx / vpieces, col = (idx - j * vpieces) * 8;
+      *reinterpret_cast<float4*>(vb + j * RV_LD + col) = make_float4(vreg[u][0], vreg[u][1], vreg[u][2], vreg[u][3]);
+      *reinterpret_cast<float4*>(vb + j * RV_LD + col + 4) = make_float4(vreg[u][4], vreg[u][5], vreg[u][6], vreg[u][7]);
+    }
+  }
+  // the first slab of S_before on its way while A V runs
   const float* sb = before + (static_cast<size_t>(slot) * heads + h) * d * dv;
+  const int spieces = dv / 4;
+  float4 sreg[8];
+  auto fetch_slab = [&](int e0) {
+    const int rows = min(RC, d - e0), total = rows * spieces;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int idx = threadIdx.x + u * blockDim.x;
+      const int e = idx / spieces, col = (idx - e * spieces) * 4;
+      sreg[u] = idx < total ? *reinterpret_cast<const float4*>(sb + static_cast<size_t>(e0 + e) * dv + col)
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  };
+  auto store_slab = [&](int e0) {
+    const int rows = min(RC, d - e0), total = rows * spieces;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int idx = threadIdx.x + u * blockDim.x;
+      if (idx < total) {
+        const int e = idx / spieces, col = (idx - e * spieces) * 4;
+        *reinterpret_cast<float4*>(vb + e * RV_LD + col) = sreg[u];
+      }
+    }
+  };
+  __syncthreads();
+  fetch_slab(0);
+  // o[i][col] for i in 4 ty .., col in 4 tx .. and 64 + 4 tx ..: A V first, then decay^(i+1) q_i^T S_before
+  float out[4][8] = {};
+  tile_product_split<4>(at, RC_LD, vb, RV_LD, RC, ty * 4, tx * 4, out);
+  float inter[4][8] = {};
   for (int e0 = 0; e0 < d; e0 += RC) {
     __syncthreads();                                            // vb is free
-    const int rows = min(RC, d - e0);
-    for (int idx = threadIdx.x; idx < rows * dv; idx += blockDim.x) {
-      const int e = idx / dv, col = idx - e * dv;
-      vb[e * RV_LD + col] = sb[static_cast<size_t>(e0 + e) * dv + col];
-    }
+    store_slab(e0);
     __syncthreads();
-    tile_product<4, 8>(qt + e0 * RC_LD, RC_LD, vb, RV_LD, rows, ty * 4, tx * 8, inter);
+    if (e0 + RC < d) fetch_slab(e0 + RC);
+    tile_product_split<4>(qt + e0 * RC_LD, RC_LD, vb, RV_LD, min(RC, d - e0), ty * 4, tx * 4, inter);
   }
 #pragma unroll
   for (int a = 0; a < 4; ++a) {
@@ -333,9 +443,12 @@ retention_chunk_kernel(const T* __restrict__ x, int in_stride, const float* __re
     const float w = pw[i] * g;                                  // decay^(i+1)
     float* dst = o + (static_cast<size_t>(t0 + i) * heads + h) * dv;
 #pragma unroll
-    for (int b = 0; b < 8; ++b) {
-      const int col = tx * 8 + b;
-      if (col < dv) dst[col] = fmaf(w, inter[a][b], out[a][b]);
+    for (int half = 0; half < 2; ++half) {
+      const int col = half * 64 + tx * 4;
+      if (col < dv)
+        *reinterpret_cast<float4*>(dst + col) =
+            make_float4(fmaf(w, inter[a][half * 4 + 0], out[a][half * 4 + 0]), fmaf(w, inter[a][half * 4 + 1], out[a][half * 4 + 1]),
+                        fmaf(w, inter[a][half * 4 + 2], out[a][half * 4 + 2]), fmaf(w, inter[a][half * 4 + 3], out[a][half * 4 + 3]));
     }
   }
 }
@@ -368,7 +481,8 @@ static int launch_chunked(const void* x, int in_stride, float* o, float* state, 
 
 // The same result as b200_retention for steps with long rows.  `max_chunks` bounds the step's chunks of 64 tokens
 // (sum over rows of ceil(tokens of the row / 64)); scratch: qf, kf [tokens, heads * d] floats, before
-// [max_chunks, heads, d, dv] floats, chunk_base [num_rows + 1] ints.  Heads up to 128 wide.
+// [max_chunks, heads, d, dv] floats, chunk_base [num_rows + 1] ints.  Heads up to 128 wide, d a multiple of 4, dv and
+// the rows of x multiples of 8.
 B200_EXPORT int b200_retention_chunked(const void* x, int dtype, int in_stride, float* o, float* state,
                                        const float* decay, const float* inv_freq, int rot_dim, float k_scale,
                                        const int* positions, const int* cu_q, const int* prefix_len,
@@ -377,7 +491,8 @@ B200_EXPORT int b200_retention_chunked(const void* x, int dtype, int in_stride, 
                                        cudaStream_t stream) {
   if (num_rows <= 0 || tokens <= 0) return 0;
   if (heads <= 0 || heads > 65535 || d <= 0 || d > RD || dv <= 0 || dv > RD || rot_dim < 0 || rot_dim > d ||
-      (rot_dim & 1) || max_chunks <= 0)
+      (rot_dim & 1) || max_chunks <= 0 || d % 4 != 0 || dv % 8 != 0 || in_stride % 8 != 0 ||
+      reinterpret_cast<uintptr_t>(x) % 16 != 0)
     return B200_BAD_SIZE;
   if (dtype == B200_F32)
     return launch_chunked<float>(x, in_stride, o, state, decay, inv_freq, rot_dim, k_scale, positions, cu_q,

@@ -10,9 +10,10 @@
 // Inputs before a row's first token of this step come from the request's state slot,
 // state[slot][taps - 1][C] in float32, oldest first; a row that starts at position 0 reads zeros, and positions
 // before the sequence's start are stored as zeros, so the state of a sequence shorter than taps - 1 is right
-// too.  The state is read by causal_taps and written by taps_state_update, a kernel of its own behind it in the
-// stream: in one kernel the block of a row's last token could overwrite what the block of its first token has
-// yet to read.  Slot 0 belongs to padding rows and may hold anything.
+// too.  The state of a row with several tokens in the step is read by causal_taps and written by taps_state_update,
+// a kernel of its own behind it in the stream: in one kernel the block of a row's last token could overwrite what
+// the block of its first token has yet to read.  A row of ONE token has one reader per channel, which writes the
+// state itself.  Slot 0 belongs to padding rows and may hold anything.
 //
 // A row's result depends on its own tokens only; sums over a token's vector are taken in a fixed order.
 #include "token_conv.cuh"
@@ -60,37 +61,18 @@ causal_taps_kernel(TapsInput<TI> in, TO* __restrict__ out, int out_stride, int i
   out[static_cast<size_t>(t) * out_stride + c] = from_f32<TO>(y);
 }
 
-// grid (rows, channel tiles of 256): new state k holds the input at position end - (taps - 1) + k
-template <typename TI>
-__global__ void __launch_bounds__(256)
-taps_state_update_kernel(TapsInput<TI> in, int num_rows) {
-  const int r = blockIdx.x;
-  const int c = blockIdx.y * blockDim.x + threadIdx.x;
-  if (c >= in.channels || r >= num_rows) return;
-  const int hist = in.taps - 1;
-  const int first = in.cu_q[r], n = in.cu_q[r + 1] - first;
-  const int prefix = in.prefix_len[r];
-  const int slot = in.state_slots[r];
-  float* st = in.state + static_cast<size_t>(slot) * hist * in.channels;
-  float fresh[TAPS_MAX - 1];
-#pragma unroll
-  for (int k = 0; k < TAPS_MAX - 1; ++k) {
-    if (k >= hist) break;
-    const int pos = prefix + n - hist + k;            // absolute position that lands in state k
-    float v = 0.0f;
-    if (pos >= prefix) {
-      const int t = first + (pos - prefix);
-      v = to_f32<TI>(in.x[static_cast<size_t>(t) * in.in_stride + c]) * (in.scale ? in.scale[t] : 1.0f);
-    } else if (pos >= 0 && prefix > 0) {
-      v = st[static_cast<size_t>(pos - prefix + hist) * in.channels + c];
-    }
-    fresh[k] = v;
-  }
-#pragma unroll
-  for (int k = 0; k < TAPS_MAX - 1; ++k) {
-    if (k >= hist) break;
-    st[static_cast<size_t>(k) * in.channels + c] = fresh[k];
-  }
+// grid (tokens, tiles of 128 x 8 channels): the same, eight channels a thread; a token that is alone in its row
+// also brings the row's state up to date (see taps_value8)
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(128)
+causal_taps_vec_kernel(TapsInput<TI> in, TO* __restrict__ out, int out_stride, int identity) {
+  const int t = blockIdx.x;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (c >= in.channels) return;
+  const TapsRow row = taps_row(in, t);
+  float y[8];
+  taps_value8(in, row, t, c, identity != 0, taps_single(in, t), y);
+  store8<TO>(out + static_cast<size_t>(t) * out_stride + c, y);
 }
 
 // ------------------------------------------------------------------ C interface
@@ -123,8 +105,26 @@ B200_EXPORT int b200_scaled_rows(void* out, int out_dtype, const float* x, const
 
 template <typename TI>
 static int launch_taps(const TapsInput<TI>& in, void* out, int out_dtype, int out_stride, int identity, int tokens,
-                       int num_rows, int update_state, cudaStream_t stream) {
+                       int num_rows, int update_state, int all_single, cudaStream_t stream) {
   const dim3 grid(tokens, (in.channels + 255) / 256);
+  const bool vec = update_state && in.channels % 8 == 0 && in.in_stride % 8 == 0 && out_stride % 8 == 0 &&
+                   (reinterpret_cast<uintptr_t>(in.x) | reinterpret_cast<uintptr_t>(out) |
+                    reinterpret_cast<uintptr_t>(in.state)) % 16 == 0;
+  if (vec) {
+    const dim3 vgrid(tokens, (in.channels / 8 + 127) / 128);
+    if (out_dtype == B200_F32)
+      causal_taps_vec_kernel<TI, float><<<vgrid, 128, 0, stream>>>(in, static_cast<float*>(out), out_stride, identity);
+    else if (out_dtype == B200_BF16)
+      causal_taps_vec_kernel<TI, __nv_bfloat16><<<vgrid, 128, 0, stream>>>(in, static_cast<__nv_bfloat16*>(out),
+                                                                          out_stride, identity);
+    else
+      return B200_BAD_DTYPE;
+    int rc = b200_check_launch();
+    if (rc != 0 || in.taps <= 1 || all_single) return rc;
+    const dim3 sgrid(num_rows, (in.channels + 255) / 256);
+    taps_state_update_kernel<TI><<<sgrid, 256, 0, stream>>>(in, num_rows, 1);
+    return b200_check_launch();
+  }
   if (out_dtype == B200_F32)
     causal_taps_kernel<TI, float><<<grid, 256, 0, stream>>>(in, static_cast<float*>(out), out_stride, identity);
   else if (out_dtype == B200_BF16)
@@ -135,7 +135,7 @@ static int launch_taps(const TapsInput<TI>& in, void* out, int out_dtype, int ou
   int rc = b200_check_launch();
   if (rc != 0 || !update_state || in.taps <= 1) return rc;
   const dim3 sgrid(num_rows, (in.channels + 255) / 256);
-  taps_state_update_kernel<TI><<<sgrid, 256, 0, stream>>>(in, num_rows);
+  taps_state_update_kernel<TI><<<sgrid, 256, 0, stream>>>(in, num_rows, 0);
   return b200_check_launch();
 }
 
@@ -151,42 +151,43 @@ static TapsInput<TI> taps_input(const void* x, int in_stride, const float* scale
 }
 
 // out[t][c] for c < channels; `x` rows are in_stride wide, `out` rows out_stride.  With update_state the rows'
-// states are brought up to date behind the convolution (a second kernel).
+// states are brought up to date: rows of one token by the convolution kernel itself where it takes eight channels
+// a thread, the others by a second kernel behind it (left out when the caller says that all rows have one token).
 B200_EXPORT int b200_causal_taps(const void* x, int in_dtype, int in_stride, const float* scale, const float* w,
                                  int taps, int channels, float* state, const int* row_of_token, const int* cu_q,
                                  const int* prefix_len, const int* state_slots, void* out, int out_dtype,
                                  int out_stride, int identity, int tokens, int num_rows, int update_state,
-                                 cudaStream_t stream) {
+                                 int all_single, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (channels <= 0 || taps < 1 || taps > TAPS_MAX || num_rows <= 0) return B200_BAD_SIZE;
   if ((channels + 255) / 256 > 65535) return B200_BAD_SIZE;
   if (in_dtype == B200_F32)
     return launch_taps<float>(taps_input<float>(x, in_stride, scale, w, taps, channels, state, row_of_token, cu_q,
                                                 prefix_len, state_slots),
-                              out, out_dtype, out_stride, identity, tokens, num_rows, update_state, stream);
+                              out, out_dtype, out_stride, identity, tokens, num_rows, update_state, all_single, stream);
   if (in_dtype == B200_BF16)
     return launch_taps<__nv_bfloat16>(taps_input<__nv_bfloat16>(x, in_stride, scale, w, taps, channels, state,
                                                                 row_of_token, cu_q, prefix_len, state_slots),
-                                      out, out_dtype, out_stride, identity, tokens, num_rows, update_state, stream);
+                                      out, out_dtype, out_stride, identity, tokens, num_rows, update_state, all_single, stream);
   return B200_BAD_DTYPE;
 }
 
 // Only the state update (for a caller whose own kernel did the convolution).
 B200_EXPORT int b200_taps_state_update(const void* x, int in_dtype, int in_stride, const float* scale, int taps,
                                        int channels, float* state, const int* cu_q, const int* prefix_len,
-                                       const int* state_slots, int num_rows, cudaStream_t stream) {
+                                       const int* state_slots, int num_rows, int skip_single, cudaStream_t stream) {
   if (num_rows <= 0 || taps <= 1) return 0;
   if (channels <= 0 || taps > TAPS_MAX || (channels + 255) / 256 > 65535) return B200_BAD_SIZE;
   const dim3 sgrid(num_rows, (channels + 255) / 256);
   if (in_dtype == B200_F32)
     taps_state_update_kernel<float><<<sgrid, 256, 0, stream>>>(
         taps_input<float>(x, in_stride, scale, nullptr, taps, channels, state, nullptr, cu_q, prefix_len, state_slots),
-        num_rows);
+        num_rows, skip_single);
   else if (in_dtype == B200_BF16)
     taps_state_update_kernel<__nv_bfloat16><<<sgrid, 256, 0, stream>>>(
         taps_input<__nv_bfloat16>(x, in_stride, scale, nullptr, taps, channels, state, nullptr, cu_q, prefix_len,
                                   state_slots),
-        num_rows);
+        num_rows, skip_single);
   else
     return B200_BAD_DTYPE;
   return b200_check_launch();

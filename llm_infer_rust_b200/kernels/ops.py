@@ -1277,6 +1277,12 @@ def scaled_rows(x: torch.Tensor, scale: torch.Tensor, rows: Optional[torch.Tenso
     return out
 
 
+def _all_single(ctx) -> int:
+    """1 when the step is known to bring every row one token (the rows' convolution states are then brought up to
+    date inside the convolution kernels and the kernel that does it for longer rows is not launched)."""
+    return int(getattr(ctx, "num_prefill", None) == 0)
+
+
 def causal_taps(x: torch.Tensor, weight: Optional[torch.Tensor], state: Optional[torch.Tensor], ctx,
                 out_dtype: torch.dtype, scale: Optional[torch.Tensor] = None, identity: bool = False,
                 channels: Optional[int] = None, update_state: bool = True) -> torch.Tensor:
@@ -1300,8 +1306,8 @@ def causal_taps(x: torch.Tensor, weight: Optional[torch.Tensor], state: Optional
     rc = _token_conv().b200_causal_taps(
         _p(x), _code(x), x.shape[1], _p(scale), _p(weight), taps, c, _p(state), _p(ctx.row_of_token), _p(ctx.cu_q),
         _p(ctx.prefix_len), _p(ctx.state_slots), _p(out), _code(out), c, int(bool(identity)), x.shape[0],
-        ctx.num_rows, int(bool(update_state)), _stream())
-    _ok(rc, "causal_taps", 2 if update_state and taps > 1 else 1)
+        ctx.num_rows, int(bool(update_state)), _all_single(ctx), _stream())
+    _ok(rc, "causal_taps", 2 if update_state and taps > 1 and not _all_single(ctx) else 1)
     return out
 
 
@@ -1314,7 +1320,7 @@ def taps_state_update(x: torch.Tensor, taps: int, channels: int, state: torch.Te
     _f32(state)
     rc = _token_conv().b200_taps_state_update(_p(x), _code(x), x.shape[1], None, taps, channels, _p(state),
                                               _p(ctx.cu_q), _p(ctx.prefix_len), _p(ctx.state_slots), ctx.num_rows,
-                                              _stream())
+                                              0, _stream())
     _ok(rc, "taps_state_update")
 
 
@@ -1325,7 +1331,8 @@ def conv_qkv_post(x: torch.Tensor, conv_weight: Optional[torch.Tensor], state: O
                   v_first: Optional[torch.Tensor] = None, v_mode: int = 0) -> None:
     """Short convolution of the packed q, k, v columns of ``x`` (state as in ``causal_taps``), rotation of q and
     k by position * inv_freq, value mixing (``v_mode`` 1: this v is written to ``v_first``; 2: v becomes
-    (1 - vmix) v + vmix v_first), q to ``q_out``, k and v into the paged cache at ``slots``."""
+    (1 - vmix) v + vmix v_first), q to ``q_out``, k and v into the paged cache at ``slots``; the rows' convolution
+    states are brought up to date."""
     _cuda(x, conv_weight, state, q_out, k_cache, v_cache, inv_freq, slots, vmix, v_first)
     _contig(x, conv_weight, state, q_out, k_cache, v_cache, inv_freq, slots, vmix, v_first)
     _f32(conv_weight, state, inv_freq, vmix, v_first)
@@ -1348,8 +1355,8 @@ def conv_qkv_post(x: torch.Tensor, conv_weight: Optional[torch.Tensor], state: O
         _p(ctx.prefix_len), _p(ctx.state_slots), _p(q_out), _p(k_cache), _p(v_cache), _p(inv_freq),
         int(rot_dim if inv_freq is not None else 0), _p(ctx.positions), _p(slots), num_heads, num_kv_heads, head_dim,
         v_head_dim, page_size, ctypes.c_longlong(k_cache.shape[0] * page_size), _p(vmix), _p(v_first), int(v_mode),
-        x.shape[0], _p(error_word(x.device)), _stream())
-    _ok(rc, "conv_qkv_post")
+        x.shape[0], ctx.num_rows, _all_single(ctx), _p(error_word(x.device)), _stream())
+    _ok(rc, "conv_qkv_post", 2 if taps > 1 and not _all_single(ctx) else 1)
 
 
 RETENTION_CHUNKED_FROM = 32        # a step whose longest row has this many tokens takes the chunked kernels
@@ -1362,7 +1369,8 @@ def retention(x: torch.Tensor, state: torch.Tensor, decay: torch.Tensor, inv_fre
     rows; q, k (rotated by position * inv_freq, k then times ``k_scale``) and v are the first columns of ``x``;
     ``state`` [slots + 1, heads, head_dim, v_head_dim] float32 is read (rows with a prefix) and written.
     Two forms with the same result up to rounding: a scan that runs the recurrence token by token (steps of short
-    rows), and, for steps with long rows and heads up to 128 wide, chunks of 64 tokens (``chunked`` forces one)."""
+    rows), and, for steps with long rows and heads up to 128 wide (whole 16-byte pieces), chunks of 64 tokens
+    (``chunked`` asks for one)."""
     _cuda(x, state, decay, inv_freq)
     _contig(x, state, decay, inv_freq)
     _f32(state, decay, inv_freq)
@@ -1373,7 +1381,8 @@ def retention(x: torch.Tensor, state: torch.Tensor, decay: torch.Tensor, inv_fre
     lib = load_cuda_library("retention.cu")
     tokens = x.shape[0]
     longest = int(getattr(ctx, "max_q_len", 0) or tokens)
-    if (chunked if chunked is not None else longest >= RETENTION_CHUNKED_FROM) and head_dim <= 128 and v_head_dim <= 128:
+    fits = head_dim <= 128 and v_head_dim <= 128 and head_dim % 4 == 0 and v_head_dim % 8 == 0 and x.shape[1] % 8 == 0
+    if (chunked if chunked is not None else longest >= RETENTION_CHUNKED_FROM) and fits:
         # long rows: the state is carried chunk by chunk and every chunk's outputs are computed on their own
         max_chunks = tokens // 64 + ctx.num_rows
         qf = torch.empty((2, tokens, heads * head_dim), dtype=torch.float32, device=x.device)

@@ -217,8 +217,6 @@ class GatedConvAttention(Part):
         ops.conv_qkv_post(packed, p.get("conv"), cache.state, ctx, q, cache.k, cache.v,
                           rope.inv_freq if rope else None, rope.rot_dim if rope else 0, slots, self.nh, self.nkv,
                           self.d, self.dv, vmix=p.get("vmix") if v_mode == 2 else None, v_first=v_first, v_mode=v_mode)
-        if self.taps > 1:
-            ops.taps_state_update(packed, self.taps, self.qkv_channels, cache.state, ctx)
         out = torch.empty((tokens, self.nh * self.dv), dtype=packed.dtype, device=packed.device)
         g = cache.group
         page = ctx.page_sizes[g]

@@ -41,12 +41,13 @@ def step_ctx(rows, device):
 
 
 # ----------------------------------------------------------------------------- mechanisms alone
+@pytest.mark.parametrize("C", [70, 72])          # rows of odd size, and rows of whole 16-byte pieces (eight channels a thread)
 @pytest.mark.parametrize("taps,identity", [(2, True), (3, True), (4, False), (8, True), (1, True)])
-def test_scaled_norm_and_causal_taps_in_portions_with_state(taps, identity):
+def test_scaled_norm_and_causal_taps_in_portions_with_state(taps, identity, C):
     from llm_infer_rust_b200.kernels import ops
     dev = torch.device("cuda")
     g = torch.Generator().manual_seed(taps)
-    C, lengths = 70, [11, 1, 6]
+    lengths = [11, 1, 6]
     w = torch.randn(C, taps, generator=g)
     gain = torch.tensor([1.3])
     xs = [torch.randn(n, C, generator=g) * 3 for n in lengths]
@@ -92,12 +93,13 @@ def test_residual_sum_is_taken_in_float():
     torch.testing.assert_close(s, torch.full((3,), 2.0 / 256.5, device=dev))
 
 
+@pytest.mark.parametrize("width", [150, 152, 9000])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_poly_norm_and_gates(dtype):
+def test_poly_norm_and_gates(dtype, width):
     from llm_infer_rust_b200.kernels import ops
     dev = torch.device("cuda")
     g = torch.Generator().manual_seed(5)
-    z = (torch.randn(7, 150, generator=g) * 2).to(dtype)
+    z = (torch.randn(7, width, generator=g) * 2).to(dtype)
     coef = torch.tensor([0.7, -1.1, 0.4, 0.25])
     got = ops.poly_norm(z.to(dev), coef.to(dev), 1e-5).float().cpu()
     want = P.poly_norm(z.double(), coef.double(), 1e-5).float()
