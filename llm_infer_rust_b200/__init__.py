@@ -1,4 +1,4 @@
-"""A single-GPU inference engine for B200 (sm_100a): dense Qwen3 first, built from
+"""A single-GPU inference engine for B200 (sm_100a): dense Qwen3 and Kefetar, built from
 parts so that another architecture is a registry entry.
 
 Public entry points:
