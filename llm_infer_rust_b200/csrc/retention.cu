@@ -239,10 +239,27 @@ retention_state_kernel(const T* __restrict__ x, int in_stride, const float* __re
     }
     __syncthreads();
     if (base + RC < n) fetch(base + RC);
-    for (int j = 0; j < L; ++j) {
-      const float v = vs[j][tx];
+    if (L == RC) {
+      // a whole chunk: eight tokens' values are fetched from shared memory before the eight dependent updates
+      for (int j0 = 0; j0 < RC; j0 += 8) {
+        float v[8], kk[8][4];
 #pragma unroll
-      for (int m = 0; m < 4; ++m) S[m] = fmaf(g, S[m], ks[j][ty + 8 * m] * v);
+        for (int u = 0; u < 8; ++u) {
+          v[u] = vs[j0 + u][tx];
+#pragma unroll
+          for (int m = 0; m < 4; ++m) kk[u][m] = ks[j0 + u][ty + 8 * m];
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+#pragma unroll
+          for (int m = 0; m < 4; ++m) S[m] = fmaf(g, S[m], kk[u][m] * v[u]);
+      }
+    } else {
+      for (int j = 0; j < L; ++j) {
+        const float v = vs[j][tx];
+#pragma unroll
+        for (int m = 0; m < 4; ++m) S[m] = fmaf(g, S[m], ks[j][ty + 8 * m] * v);
+      }
     }
     __syncthreads();
   }
