@@ -6,6 +6,7 @@
 //   causal_taps      y[t][c] = (identity ? u[t][c] : 0) + sum_j w[c][j] * u[t - taps + 1 + j][c],
 //                    u[t][c] = in[t][c] * (s ? s[t] : 1)
 //   taps_state_update   the last taps - 1 inputs u of every row become the row's state
+//   add_norm_taps_single   the first, the third and the fourth in one kernel, for steps whose rows have one token
 //
 // Inputs before a row's first token of this step come from the request's state slot,
 // state[slot][taps - 1][C] in float32, oldest first; a row that starts at position 0 reads zeros, and positions
@@ -73,6 +74,43 @@ causal_taps_vec_kernel(TapsInput<TI> in, TO* __restrict__ out, int out_stride, i
   float y[8];
   taps_value8(in, row, t, c, identity != 0, taps_single(in, t), y);
   store8<TO>(out + static_cast<size_t>(t) * out_stride + c, y);
+}
+
+// ------------------------------------------------------------------ a step whose rows all have one token
+// x[t] += y[t], the norm's scale, the convolution and the row's new state in one kernel, a block a token: no token
+// of the step is another token's past, so nothing that one block writes is read by another.
+template <typename TY, typename TO>
+__global__ void __launch_bounds__(256)
+add_norm_taps_single_kernel(float* x /* also read through `in` */, const TY* __restrict__ y, const float* __restrict__ gain, float eps,
+                            float* __restrict__ scale, TapsInput<float> in, TO* __restrict__ out, int out_stride,
+                            int identity) {
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  const int width = in.channels;
+  const size_t base = static_cast<size_t>(t) * width;
+  float ss = 0.0f;
+  for (int c = threadIdx.x * 8; c < width; c += blockDim.x * 8) {
+    float v[8];
+    load_floats<float, 8>(x + base + c, v);
+    if (y != nullptr) {
+      float a[8];
+      load_floats<TY, 8>(y + base + c, a);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] += a[i];
+      store8<float>(x + base + c, v);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
+  }
+  ss = block_sum(ss, scratch);
+  if (threadIdx.x == 0) scale[t] = gain[0] / sqrtf(ss / static_cast<float>(width) + eps);
+  __syncthreads();                                   // the scale, and every thread's own x, are read back below
+  const TapsRow row = taps_row(in, t);
+  for (int c = threadIdx.x * 8; c < width; c += blockDim.x * 8) {
+    float r[8];
+    taps_value8(in, row, t, c, identity != 0, true, r);
+    store8<TO>(out + static_cast<size_t>(t) * out_stride + c, r);
+  }
 }
 
 // ------------------------------------------------------------------ C interface
@@ -190,5 +228,36 @@ B200_EXPORT int b200_taps_state_update(const void* x, int in_dtype, int in_strid
         num_rows, skip_single);
   else
     return B200_BAD_DTYPE;
+  return b200_check_launch();
+}
+
+// The fused form for a step whose rows ALL bring one token (the caller vouches for it): x += y (y may be null), scale
+// [tokens] and out [tokens, channels] as b200_residual_scale and b200_causal_taps (with update_state) leave them.
+// Refuses (B200_BAD_SIZE / B200_BAD_ALIGN) rows that are no whole 16-byte pieces; the caller then runs the two.
+B200_EXPORT int b200_add_norm_taps_single(float* x, const void* y, int y_dtype, const float* gain, float eps,
+                                          float* scale, const float* w, int taps, int channels, float* state,
+                                          const int* row_of_token, const int* cu_q, const int* prefix_len,
+                                          const int* state_slots, void* out, int out_dtype, int identity, int tokens,
+                                          cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (channels <= 0 || channels % 8 != 0 || taps < 1 || taps > TAPS_MAX) return B200_BAD_SIZE;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(out) |
+       reinterpret_cast<uintptr_t>(state) | reinterpret_cast<uintptr_t>(w)) % 16 != 0)
+    return B200_BAD_ALIGN;
+  const TapsInput<float> in = taps_input<float>(x, channels, scale, w, taps, channels, state, row_of_token, cu_q,
+                                                prefix_len, state_slots);
+#define B200_FUSED(TY, TO)                                                                                          \
+  add_norm_taps_single_kernel<TY, TO><<<tokens, 256, 0, stream>>>(x, static_cast<const TY*>(y), gain, eps, scale, in, \
+                                                                   static_cast<TO*>(out), channels, identity)
+  const bool y32 = y == nullptr || y_dtype == B200_F32;
+  if (!y32 && y_dtype != B200_BF16) return B200_BAD_DTYPE;
+  if (out_dtype == B200_F32) {
+    if (y32) B200_FUSED(float, float); else B200_FUSED(__nv_bfloat16, float);
+  } else if (out_dtype == B200_BF16) {
+    if (y32) B200_FUSED(float, __nv_bfloat16); else B200_FUSED(__nv_bfloat16, __nv_bfloat16);
+  } else {
+    return B200_BAD_DTYPE;
+  }
+#undef B200_FUSED
   return b200_check_launch();
 }

@@ -105,7 +105,7 @@ __device__ __forceinline__ void taps_value8_n(const TapsInput<T>& in, const Taps
     return;
   }
   const int taps = TAPS > 0 ? TAPS : in.taps, hist = taps - 1;
-  float wl[TAPS > 0 ? 8 * TAPS : 1];
+  float wl[TAPS > 0 ? 8 * TAPS : 1] = {};
   if constexpr (TAPS > 0) load_floats<float, 8 * TAPS>(in.w + static_cast<size_t>(c) * TAPS, wl);
   auto weight = [&](int i, int j) { return TAPS > 0 ? wl[i * (TAPS > 0 ? TAPS : 1) + j] : in.w[static_cast<size_t>(c + i) * taps + j]; };
   float* st = const_cast<float*>(row.state);

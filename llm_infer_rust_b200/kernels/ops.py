@@ -1311,6 +1311,32 @@ def causal_taps(x: torch.Tensor, weight: Optional[torch.Tensor], state: Optional
     return out
 
 
+def add_norm_taps_single(x: torch.Tensor, y: Optional[torch.Tensor], gain: torch.Tensor, eps: float,
+                         weight: torch.Tensor, state: Optional[torch.Tensor], ctx, out_dtype: torch.dtype,
+                         identity: bool) -> Optional[torch.Tensor]:
+    """``residual_scale`` and ``causal_taps`` in one kernel, for a step whose rows all bring ONE token (a decode
+    step): x += y, the one-gain norm's scale, the convolution over the normed rows, the rows' states.  None when
+    the step has longer rows or the rows are no whole 16-byte pieces: the caller then runs the two."""
+    taps = weight.shape[1]
+    if not _all_single(ctx) or x.shape[1] % 8 or (taps > 1 and state is None):
+        return None
+    _cuda(x, y, gain, weight, state)
+    _contig(x, y, gain, weight, state)
+    _f32(x, gain, weight, state)
+    if weight.shape[0] != x.shape[1] or (taps > 1 and tuple(state.shape[1:]) != (taps - 1, x.shape[1])):
+        raise KernelError("the taps must be [channels, taps] and the state [slots + 1, taps - 1, channels]")
+    scale = torch.empty(x.shape[0], dtype=torch.float32, device=x.device)
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    rc = _token_conv().b200_add_norm_taps_single(
+        _p(x), _p(y), _code(y) if y is not None else F32, _p(gain), ctypes.c_float(eps), _p(scale), _p(weight), taps,
+        x.shape[1], _p(state), _p(ctx.row_of_token), _p(ctx.cu_q), _p(ctx.prefix_len), _p(ctx.state_slots), _p(out),
+        _code(out), int(bool(identity)), x.shape[0], _stream())
+    if rc in (-2, -3):
+        return None
+    _ok(rc, "add_norm_taps_single")
+    return out
+
+
 def taps_state_update(x: torch.Tensor, taps: int, channels: int, state: torch.Tensor, ctx) -> None:
     """The last ``taps - 1`` rows of x (first ``channels`` columns) of every row of the step become its state."""
     if taps <= 1:

@@ -109,6 +109,12 @@ class PreNormInputConv:
         return specs
 
     def _read(self, norm, conv, name, x, add, ctx, cache):
+        if conv is not None and hasattr(conv, "forward_after_norm") and hasattr(norm, "eps"):
+            # a decode step: add, norm, convolution and state in one kernel
+            fused = conv.forward_after_norm(x, add, norm.params["weight"], norm.eps, ctx, cache.states.get(name),
+                                            self.env.dtype)
+            if fused is not None:
+                return fused
         scale = norm.scale(x, add)                     # x += add, in float
         if conv is None:
             return ops.scaled_rows(x, scale, None, self.env.dtype)

@@ -34,6 +34,11 @@ class CausalTaps(Part):
     def state_spec(self):
         return StateSpec((self.taps - 1, self.channels), torch.float32) if self.taps > 1 else None
 
+    def forward_after_norm(self, x, add, gain, eps, ctx, state, out_dtype):
+        """x += add, a one-gain RMS norm of x and this convolution over it in one kernel, where the step allows it
+        (every row one token); None otherwise."""
+        return ops.add_norm_taps_single(x, add, gain, eps, self.params["weight"], state, ctx, out_dtype, self.identity)
+
     def forward(self, x, scale, ctx, state, out_dtype):
         return ops.causal_taps(x, self.params["weight"], state, ctx, out_dtype, scale=scale, identity=self.identity)
 

@@ -83,6 +83,39 @@ def test_scaled_norm_and_causal_taps_in_portions_with_state(taps, identity, C):
         torch.testing.assert_close(torch.cat(got[r]).double(), want[r], rtol=1e-5, atol=1e-5)
 
 
+@pytest.mark.parametrize("taps", [1, 3, 5])
+def test_add_norm_and_taps_in_one_kernel_for_rows_of_one_token(taps):
+    """Three sequences decoded side by side, token by token, through the fused kernel; a fourth step that has a longer
+    row is refused by it (None) and the fused steps leave the states as the two kernels would."""
+    from llm_infer_rust_b200.kernels import ops
+    dev = torch.device("cuda")
+    g = torch.Generator().manual_seed(taps)
+    C, T = 64, 7
+    w, gain = torch.randn(C, taps, generator=g), torch.tensor([0.8])
+    xs = torch.randn(3, T, C, generator=g) * 2
+    ys = (torch.randn(3, T, C, generator=g)).to(torch.bfloat16)
+    state = torch.full((5, max(taps - 1, 0), C), 3.0, device=dev)
+    slots = [4, 1, 2]
+    got = []
+    for t in range(T):
+        ctx = step_ctx([(slots[r], t, 1) for r in range(3)], dev)
+        ctx.num_prefill = 0
+        x = xs[:, t].to(dev).contiguous()
+        out = ops.add_norm_taps_single(x, ys[:, t].to(dev).contiguous(), gain.to(dev), 1e-5, w.to(dev),
+                                       state if taps > 1 else None, ctx, torch.float32, True)
+        assert out is not None
+        torch.testing.assert_close(x.cpu(), xs[:, t] + ys[:, t].float())
+        got.append(out.cpu())
+    got = torch.stack(got, 1)
+    for r in range(3):
+        h = P.scalar_rms_norm((xs[r] + ys[r].float()).double(), gain.double(), 1e-5)
+        torch.testing.assert_close(got[r].double(), P.canon(h, w.double()), rtol=1e-5, atol=1e-5)
+    ctx = step_ctx([(1, 0, 2)], dev)
+    ctx.num_prefill = 1
+    assert ops.add_norm_taps_single(xs[0, :2].to(dev).contiguous(), None, gain.to(dev), 1e-5, w.to(dev),
+                                    state if taps > 1 else None, ctx, torch.float32, True) is None
+
+
 def test_residual_sum_is_taken_in_float():
     from llm_infer_rust_b200.kernels import ops
     dev = torch.device("cuda")
@@ -307,3 +340,32 @@ def test_trace_replay_as_a_user_runs_it(models, tmp_path):
             K.check(run_alone(rp, "x", ids, [33, 2, 3] + [1] * 32), want, dtype, "replay")
         finally:
             assert rp.close() == 0
+
+
+def test_command_line_random_weights_mode_and_sampling(tmp_path):
+    """The command line writes a random Kefetar model from a configuration and serves it; the same folder through
+    ``Engine.generate`` gives the same tokens, and sampled generation repeats itself under a seed."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from llm_infer_rust_b200 import SamplingParams
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = tmp_path / "cfg.json"
+    cfg.write_text(json.dumps(K.CONFIGS["K2"]))
+    made = tmp_path / "made"
+    cmd = [sys.executable, "-m", "llm_infer_rust_b200", "--model-path", str(made), "--random-weights", "--config",
+           str(cfg), "--seed", "5", "--dtype", "float32", "--page-size", "4", "--max-total-tokens", "256",
+           "--max-running-req", "2", "--max-seq-len", "64", "--cuda-graph-bs", "0", "--prompt-ids", "1,2,3",
+           "--prompt-ids", "9,8,7,6,5", "--max-tokens", "6", "--ignore-eos"]
+    done = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr
+    lines = [json.loads(x) for x in done.stdout.strip().splitlines()]
+    assert sorted(os.listdir(made)) == ["config.json", "model.safetensors"]
+    eng = K.make_engine(str(made), "float32", page_size=4, pool_tokens=256, max_requests=2)
+    want = eng.generate([[1, 2, 3], [9, 8, 7, 6, 5]], SamplingParams(max_tokens=6, ignore_eos=True))
+    assert [x["output_ids"] for x in lines] == [r.tokens for r in want]
+    sp = SamplingParams(temperature=0.9, top_k=12, top_p=0.95, max_tokens=8, ignore_eos=True, seed=3)
+    first = eng.generate([[4, 4, 4]], sp)[0].tokens
+    assert eng.generate([[4, 4, 4]], sp)[0].tokens == first and len(first) == 8
+    eng.check_kernel_errors()
