@@ -20,7 +20,7 @@ def kefetar_weight_plan(c: KefetarConfig) -> List[WeightBinding]:
     for i, l in enumerate(c.layers):
         src, dst = f"l{i}.", f"layers.{i}."
         plan.append(WeightBinding(dst + "input_norm.weight", (SourceTensor(src + "norm1", (), "norm"),)))
-        if c.canon_taps > 1:
+        if c.canon_taps >= 1:
             plan.append(WeightBinding(dst + "mixer_conv.weight", (SourceTensor(src + "canon1", (w, c.canon_taps)),)))
         kv = l.kv_heads if l.kind == "attention" else l.heads
         q_rows, k_rows, v_rows, g_rows = l.heads * l.dim, kv * l.dim, kv * l.vdim, l.heads * l.vdim
@@ -29,7 +29,7 @@ def kefetar_weight_plan(c: KefetarConfig) -> List[WeightBinding]:
             SourceTensor(src + "mix.v", (v_rows, w)), SourceTensor(src + "mix.g", (g_rows, w)))))
         plan.append(WeightBinding(dst + "mixer.o_proj", (SourceTensor(src + "mix.o", (w, g_rows)),)))
         if l.kind == "attention":
-            if l.conv > 1:
+            if l.conv >= 1:
                 plan.append(WeightBinding(dst + "mixer.conv", (
                     SourceTensor(src + "mix.q.conv", (q_rows, l.conv)), SourceTensor(src + "mix.k.conv", (k_rows, l.conv)),
                     SourceTensor(src + "mix.v.conv", (v_rows, l.conv)))))
@@ -37,7 +37,7 @@ def kefetar_weight_plan(c: KefetarConfig) -> List[WeightBinding]:
                 plan.append(WeightBinding(dst + "mixer.vmix", (SourceTensor(src + "mix.vmix", ()),)))
         if l.ff is not None:
             plan.append(WeightBinding(dst + "post_mixer_norm.weight", (SourceTensor(src + "norm2", (), "norm"),)))
-            if c.canon_taps > 1:
+            if c.canon_taps >= 1:
                 plan.append(WeightBinding(dst + "ff_conv.weight", (SourceTensor(src + "canon2", (w, c.canon_taps)),)))
             plan += [WeightBinding(dst + "feed_forward.up_proj", (SourceTensor(src + "mlp.up", (l.ff, w)),)),
                      WeightBinding(dst + "feed_forward.down_proj", (SourceTensor(src + "mlp.down", (w, l.ff)),)),

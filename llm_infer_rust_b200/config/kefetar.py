@@ -4,7 +4,7 @@
     vocab, width   sizes of the embedding table and of the residual stream
     norm.eps       eps of every RMS norm of the model (inside the root)
     canon.taps     taps of the causal convolution through which every sublayer reads its normed input
-                   (absent or 1: no such convolution)
+                   (absent: no such convolution; 1: a gain per channel)
     layers[i]      type ("attention" | "retention"), mixer (sizes and constants, below), mlp (null, or
                    {"kind": "dense", "ff": F})
 
@@ -63,7 +63,7 @@ class KefetarLayer:
     ff: Optional[int]                      # None: no feed-forward sublayer
     # attention
     kv_heads: int = 0
-    conv: int = 1
+    conv: int = 0                          # taps of the q/k/v convolution, 0: none
     scale: float = 1.0
     softcap: Optional[float] = None
     v_mix: bool = False
@@ -76,7 +76,7 @@ class KefetarConfig:
     vocab: int
     width: int
     eps: float
-    canon_taps: int
+    canon_taps: int                        # 0: sublayers read the normed input itself
     layers: Tuple[KefetarLayer, ...]
 
     architecture = "Kefetar"
@@ -110,7 +110,7 @@ class KefetarConfig:
             raise ConfigError("missing norm (an object with eps)")
         eps = _number(norm, "eps", "norm.")
         canon = raw.get("canon")
-        canon_taps = 1
+        canon_taps = 0
         if canon is not None:
             if not isinstance(canon, dict):
                 raise ConfigError("invalid canon: an object is required")
@@ -142,7 +142,7 @@ class KefetarConfig:
                     raise ConfigError(f"{where}mixer: dim and vdim must be even and at most 512")
                 layers.append(KefetarLayer(
                     "attention", heads, dim, vdim, rot, ff, kv_heads=kv_heads,
-                    conv=_int(m, "conv", where + "mixer.") if m.get("conv") is not None else 1,
+                    conv=_int(m, "conv", where + "mixer.") if m.get("conv") is not None else 0,
                     scale=_number(m, "scale", where + "mixer."),
                     softcap=_number(m, "softcap", where + "mixer.") if m.get("softcap") is not None else None,
                     v_mix=bool(m.get("v_mix", False))))
@@ -178,7 +178,7 @@ class KefetarConfig:
                     "rotary_dim": rot.dims, "theta": rot.base, "scaling_factor": rot.factor})
             return names[rot]
 
-        canon = PartSpec("causal_taps", {"channels": self.width, "taps": self.canon_taps, "identity": True})
+        canon = PartSpec("causal_taps", {"channels": self.width, "taps": max(self.canon_taps, 1), "identity": True})
         layers = []
         seen_v_mix = False
         for l in self.layers:
@@ -197,13 +197,13 @@ class KefetarConfig:
                     "decay": l.decay, "eps": self.eps, "k_scale": l.dim ** -0.5,
                     "position_encoding": encoding(l.rot)})
             parts = {"input_norm": norm, "mixer": mixer}
-            if self.canon_taps > 1:
+            if self.canon_taps >= 1:
                 parts["mixer_conv"] = canon
             if l.ff is not None:
                 parts["post_mixer_norm"] = norm
                 parts["feed_forward"] = PartSpec("poly_norm", {"hidden_size": self.width, "intermediate_size": l.ff,
                                                                "eps": self.eps})
-                if self.canon_taps > 1:
+                if self.canon_taps >= 1:
                     parts["ff_conv"] = canon
             layers.append(LayerSpec(PartSpec("pre_norm_input_conv"), parts))
         spec = ModelSpec(

@@ -133,7 +133,7 @@ class GatedConvAttention(Part):
 
     q, k, v, g = x W^T (one packed matrix: q rows, k rows, v rows, gate rows; keys are ``head_dim`` wide, values
     ``v_head_dim``); then, each optional and a parameter of the part:
-      * ``conv_taps`` > 1: a causal convolution on every channel of q, k and v (``conv`` [channels, taps]; its
+      * ``conv_taps`` >= 1: a causal convolution on every channel of q, k and v (``conv`` [channels, taps]; its
         last taps - 1 inputs are the request's state);
       * ``position_encoding``: half-split rotation of q and k;
       * ``v_mix`` "source": this layer's v is kept for the step under the name ``v_mix_group``; "mix": v becomes
@@ -152,7 +152,7 @@ class GatedConvAttention(Part):
         self.nkv = int(spec["num_kv_heads"])
         self.d = int(spec["head_dim"])
         self.dv = int(spec.get("v_head_dim") or self.d)
-        self.taps = int(spec.get("conv_taps") or 1)
+        self.taps = int(spec.get("conv_taps") or 0)           # 0: no convolution; 1: a gain per channel
         self.window = spec.get("window")
         self.scale = float(spec.get("softmax_scale", 1.0 / math.sqrt(self.d)))
         self.softcap = float(spec.get("softcap") or 0.0)
@@ -166,8 +166,8 @@ class GatedConvAttention(Part):
         for width in (self.d, self.dv):
             if width % 2 or not 2 <= width <= 512:
                 raise ValueError(f"head size {width} is refused: the attention kernels take even head sizes up to 512")
-        if not 1 <= self.taps <= 8:
-            raise ValueError(f"{self.taps} taps are refused: the convolution kernels take 1 to 8")
+        if not 0 <= self.taps <= 8:
+            raise ValueError(f"{self.taps} taps are refused: the convolution kernels take up to 8")
         name = spec.get("position_encoding")
         self.rope = env.position_encodings[name] if name else None
         if self.rope is not None and self.rope.rot_dim > self.d:
@@ -177,7 +177,7 @@ class GatedConvAttention(Part):
     def param_decls(self):
         rows = self.qkv_channels + (self.nh * self.dv if self.gate else 0)
         decls = {"qkvg_proj": ParamDecl((rows, self.hidden)), "o_proj": ParamDecl((self.hidden, self.nh * self.dv))}
-        if self.taps > 1:
+        if self.taps >= 1:
             decls["conv"] = ParamDecl((self.qkv_channels, self.taps))
         if self.v_mix is not None:
             decls["vmix"] = ParamDecl((), "vector")

@@ -70,11 +70,18 @@ CONFIGS = {
     ], canon_taps=2),
 }
 
-# One mixer alone, the attention one with scores so sharp that a single key decides a position's result.
-ONLY_ATTENTION = config(89, 32, 1e-5, [
+# convolutions of ONE tap (a gain per channel, no state), a layer order that ends on retention without feed-forward
+CONFIGS["K4"] = config(61, 24, 1e-5, [
+    attention(2, 1, 8, 8, 0.35, conv=1, rot={"base": 10.0, "dims": 8}, ff=16),
+    retention(2, 8, 8, [0.9, 0.8]),
+], canon_taps=1)
+
+# One mixer alone, the attention one with scores so sharp that a single key decides a position's result; widths
+# that are no whole 16-byte pieces (the kernels' one-channel-a-thread forms).
+ONLY_ATTENTION = config(89, 34, 1e-5, [
     attention(4, 2, 16, 12, 3.0, conv=3, rot={"base": 100.0, "dims": 8, "scaling": {"factor": 2.0}}, softcap=30.0)],
     canon_taps=3)
-ONLY_RETENTION = config(89, 32, 1e-5, [
+ONLY_RETENTION = config(89, 36, 1e-5, [
     retention(2, 16, 24, [0.999, 0.9995], rot={"base": 100.0, "dims": 16})], canon_taps=3)
 
 
@@ -90,7 +97,7 @@ def random_weights(raw: dict, seed: int) -> Dict[str, torch.Tensor]:
         return bf16_values(mean + std * torch.randn(tuple(shape), generator=g))
 
     w, width = {}, raw["width"]
-    taps = (raw.get("canon") or {}).get("taps", 1)
+    taps = (raw.get("canon") or {}).get("taps", 0)
     w["embed"] = normal(raw["vocab"], width)
     w["head"] = normal(raw["vocab"], width, std=width ** -0.5)
     w["final.norm"] = normal(std=0.1, mean=1.0)
@@ -99,13 +106,13 @@ def random_weights(raw: dict, seed: int) -> Dict[str, torch.Tensor]:
         kv = m.get("kv_heads", m["heads"])
         rows = {"q": m["heads"] * m["dim"], "k": kv * m["dim"], "v": kv * m["vdim"], "g": m["heads"] * m["vdim"]}
         w[p + "norm1"] = normal(std=0.2, mean=1.0)
-        if taps > 1:
+        if taps >= 1:
             w[p + "canon1"] = normal(width, taps, std=0.4)
         for name, n in rows.items():
             w[p + "mix." + name] = normal(n, width, std=width ** -0.5 * (2.0 if name in "qk" else 1.0))
         w[p + "mix.o"] = normal(width, rows["g"], std=rows["g"] ** -0.5)
         if layer["type"] == "attention":
-            if m.get("conv", 1) > 1:
+            if m.get("conv", 0) >= 1:
                 for name in "qkv":
                     w[p + f"mix.{name}.conv"] = normal(rows[name], m["conv"], std=0.6)
             if m.get("v_mix"):
@@ -113,7 +120,7 @@ def random_weights(raw: dict, seed: int) -> Dict[str, torch.Tensor]:
         if layer.get("mlp"):
             ff = layer["mlp"]["ff"]
             w[p + "norm2"] = normal(std=0.2, mean=1.0)
-            if taps > 1:
+            if taps >= 1:
                 w[p + "canon2"] = normal(width, taps, std=0.4)
             w[p + "mlp.up"] = normal(ff, width, std=width ** -0.5)
             w[p + "mlp.down"] = normal(width, ff, std=ff ** -0.5)

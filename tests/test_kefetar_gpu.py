@@ -226,7 +226,7 @@ def cut(total, pattern):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["K1", "K2", "K3", "attention", "retention"])
+@pytest.mark.parametrize("name", ["K1", "K2", "K3", "K4", "attention", "retention"])
 def test_whole_decoded_and_in_portions(name, dtype, models):
     raw, w, folder = models[name]
     T = 150

@@ -31,7 +31,9 @@ def test_the_architecture_is_found_by_its_name_and_every_size_comes_from_the_fil
     assert all("mixer_conv" not in l.parts for l in spec2.layers)
     m = spec2.layers[0]["mixer"]
     assert m.get("softcap") is None and m.get("position_encoding") is None and m.get("v_mix") is None
-    assert m["conv_taps"] == 4 and spec2.layers[2]["mixer"]["conv_taps"] == 1
+    assert m["conv_taps"] == 4 and spec2.layers[2]["mixer"]["conv_taps"] == 0
+    one = arch.model_spec(arch.parse_config(K.CONFIGS["K4"]))                 # one tap is a convolution too
+    assert one.layers[0]["mixer"]["conv_taps"] == 1 and one.layers[0]["mixer_conv"]["taps"] == 1
 
 
 @pytest.mark.parametrize("change,message", [
