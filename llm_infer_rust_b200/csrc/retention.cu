@@ -147,14 +147,15 @@ static int dispatch_scan(const void* x, int in_stride, float* o, float* state, c
 }
 
 // ------------------------------------------------------------------ prompt portions, in chunks of 64 tokens
-// Three kernels.  (1) retention_rotate_kernel: q and k of every token rotated once (k also scaled) into float
-// buffers qf, kf [tokens, heads * d].  (2) retention_state_kernel: grid (rows, heads, 32 x 32 tiles of the
-// state); a block walks its row's chunks in order, leaves its tile of the state as it stood BEFORE each chunk in
-// `before` [chunk slot, heads, d, dv], runs the recurrence S <- decay S + k v^T over the chunk's tokens one by
-// one, and writes the row's final state.  (3) retention_chunk_kernel: grid (chunk slots, heads), every chunk on
-// its own:   o_i = decay^(i+1) q_i^T S_before + sum over j <= i of decay^(i-j) (q_i . k_j) v_j
+// Four kernels.  (1) retention_rotate_kernel: q and k of every token rotated once (k also scaled) into float
+// buffers qf, kf [tokens, heads * d].  (2a) retention_chunk_sum_kernel: every chunk's own contribution to the state,
+// all chunks at once; (2b) retention_fold_kernel: chunk by chunk, element by element, the state as it stands
+// BEFORE each chunk is left in `before` [chunk slot, heads, d, dv] and the row's final state is written.
+// (3) retention_chunk_kernel: grid (chunk slots, heads), every chunk on its own:
+//     o_i = decay^(i+1) q_i^T S_before + sum over j <= i of decay^(i-j) (q_i . k_j) v_j
 // as two small float products in shared memory (A = Q K^T with the decays, then [A | Q diag] [V ; S_before]).
 // Chunk slots of row r start at chunk_base[r] (a prefix sum on the device, made by retention_chunk_base_kernel).
+// The state after a portion differs from the token-by-token recurrence by the order of float additions only.
 constexpr int RC = 64;         // tokens of a chunk
 constexpr int RD = 128;        // widest head (keys and values) of the chunked path
 
@@ -186,88 +187,99 @@ __global__ void retention_chunk_base_kernel(const int* __restrict__ cu_q, int nu
   }
 }
 
+// (2a) A block owns a 32 x 64 tile of one chunk's own contribution U = sum over j < L of decay^(L-1-j) k_j v_j^T;
+// a thread 4 rows (4 ty ..) of 2 columns (2 tx, 2 tx + 1).  k is multiplied by its power of the decay as it is
+// staged, so a token costs a thread one 16-byte load of k that the whole warp shares, one 8-byte load of v and
+// 8 FMAs.  U goes where the state before the chunk will stand (`before`); (2b) folds the chunks together.
+constexpr int RS_I = 32, RS_J = 64;
 template <typename T>
 __global__ void __launch_bounds__(256)
-retention_state_kernel(const T* __restrict__ x, int in_stride, const float* __restrict__ kf, float* __restrict__ before,
-                       float* __restrict__ state, const float* __restrict__ decay, const int* __restrict__ cu_q,
-                       const int* __restrict__ prefix_len, const int* __restrict__ state_slots,
-                       const int* __restrict__ chunk_base, int heads, int d, int dv) {
-  __shared__ float ks[RC][33];
-  __shared__ float vs[RC][33];
-  const int r = blockIdx.x, h = blockIdx.y;
-  const int tiles_v = (dv + 31) / 32;
-  const int ti = blockIdx.z / tiles_v, tj = blockIdx.z - ti * tiles_v;
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;            // column, and rows ty + 8 m
-  const int col = tj * 32 + tx;
+retention_chunk_sum_kernel(const T* __restrict__ x, int in_stride, const float* __restrict__ kf,
+                           float* __restrict__ before, const float* __restrict__ decay, const int* __restrict__ cu_q,
+                           const int* __restrict__ chunk_base, int num_rows, int heads, int d, int dv) {
+  __shared__ __align__(16) float ks[RC][RS_I + 4];
+  __shared__ __align__(16) float vs[RC][RS_J + 2];
+  const int slot = blockIdx.x, h = blockIdx.y;
+  if (slot >= chunk_base[num_rows]) return;
+  int r = 0;
+  while (chunk_base[r + 1] <= slot) ++r;
   const int first = cu_q[r], n = cu_q[r + 1] - first;
-  const float g = decay[h];
-  float* st = state + (static_cast<size_t>(state_slots[r]) * heads + h) * d * dv;
-  const bool has_past = prefix_len[r] > 0;
+  const int base = (slot - chunk_base[r]) * RC;
+  const int L = min(RC, n - base);
+  const int tiles_v = (dv + RS_J - 1) / RS_J;
+  const int ti = blockIdx.z / tiles_v, tj = blockIdx.z - ti * tiles_v;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int col = tj * RS_J + 2 * tx, row0 = ti * RS_I + 4 * ty;
+  const float lg = log2f(decay[h]);
   const int voff = 2 * heads * d + h * dv;
-  float S[4];
+  const bool k_ok = ti * RS_I + tx < d, v0_ok = tj * RS_J + tx < dv, v1_ok = tj * RS_J + 32 + tx < dv;
+  const float* kcol = kf + static_cast<size_t>(h) * d + ti * RS_I + tx;
+  const T* vcol = x + voff + tj * RS_J + tx;
 #pragma unroll
-  for (int m = 0; m < 4; ++m) {
-    const int i = ti * 32 + ty + 8 * m;
-    S[m] = (has_past && i < d && col < dv) ? st[static_cast<size_t>(i) * dv + col] : 0.0f;
+  for (int m = 0; m < 8; ++m) {
+    const int j = ty + 8 * m;
+    const size_t t = static_cast<size_t>(first + base + j);
+    const float w = L - 1 - j == 0 ? 1.0f : exp2f(static_cast<float>(L - 1 - j) * lg);
+    ks[j][tx] = (j < L && k_ok) ? kcol[t * heads * d] * w : 0.0f;
+    vs[j][tx] = (j < L && v0_ok) ? to_f32<T>(vcol[t * in_stride]) : 0.0f;
+    vs[j][tx + 32] = (j < L && v1_ok) ? to_f32<T>(vcol[t * in_stride + 32]) : 0.0f;
   }
-  // A thread stages k and v of tokens ty + 8 m (m < 8) of a chunk, element tx of the tile's 32: the next chunk's
-  // values are fetched into registers while the recurrence runs over the current chunk.
-  const bool k_ok = ti * 32 + tx < d, v_ok = col < dv;
-  const float* kcol = kf + static_cast<size_t>(h) * d + ti * 32 + tx;
-  const T* vcol = x + voff + col;
-  float kn[8], vn[8];
-  auto fetch = [&](int base) {
-    const int L = min(RC, n - base);
-#pragma unroll
-    for (int m = 0; m < 8; ++m) {
-      const int j = ty + 8 * m;
-      const size_t t = static_cast<size_t>(first + base + j);
-      kn[m] = (j < L && k_ok) ? kcol[t * heads * d] : 0.0f;
-      vn[m] = (j < L && v_ok) ? to_f32<T>(vcol[t * in_stride]) : 0.0f;
-    }
-  };
-  if (n > 0) fetch(0);
-  for (int base = 0, c = chunk_base[r]; base < n; base += RC, ++c) {
-    const int L = min(RC, n - base);
-#pragma unroll
-    for (int m = 0; m < 8; ++m) { ks[ty + 8 * m][tx] = kn[m]; vs[ty + 8 * m][tx] = vn[m]; }
-    float* dst = before + (static_cast<size_t>(c) * heads + h) * d * dv;
-#pragma unroll
-    for (int m = 0; m < 4; ++m) {
-      const int i = ti * 32 + ty + 8 * m;
-      if (i < d && col < dv) dst[static_cast<size_t>(i) * dv + col] = S[m];
-    }
-    __syncthreads();
-    if (base + RC < n) fetch(base + RC);
-    if (L == RC) {
-      // a whole chunk: eight tokens' values are fetched from shared memory before the eight dependent updates
-      for (int j0 = 0; j0 < RC; j0 += 8) {
-        float v[8], kk[8][4];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          v[u] = vs[j0 + u][tx];
-#pragma unroll
-          for (int m = 0; m < 4; ++m) kk[u][m] = ks[j0 + u][ty + 8 * m];
-        }
-#pragma unroll
-        for (int u = 0; u < 8; ++u)
-#pragma unroll
-          for (int m = 0; m < 4; ++m) S[m] = fmaf(g, S[m], kk[u][m] * v[u]);
-      }
-    } else {
-      for (int j = 0; j < L; ++j) {
-        const float v = vs[j][tx];
-#pragma unroll
-        for (int m = 0; m < 4; ++m) S[m] = fmaf(g, S[m], ks[j][ty + 8 * m] * v);
-      }
-    }
-    __syncthreads();
+  __syncthreads();
+  float U[4][2] = {};
+#pragma unroll 8
+  for (int j = 0; j < RC; ++j) {                    // rows beyond L hold zeros
+    const float4 k4 = *reinterpret_cast<const float4*>(&ks[j][4 * ty]);
+    const float2 v2 = *reinterpret_cast<const float2*>(&vs[j][2 * tx]);
+    U[0][0] = fmaf(k4.x, v2.x, U[0][0]); U[0][1] = fmaf(k4.x, v2.y, U[0][1]);
+    U[1][0] = fmaf(k4.y, v2.x, U[1][0]); U[1][1] = fmaf(k4.y, v2.y, U[1][1]);
+    U[2][0] = fmaf(k4.z, v2.x, U[2][0]); U[2][1] = fmaf(k4.z, v2.y, U[2][1]);
+    U[3][0] = fmaf(k4.w, v2.x, U[3][0]); U[3][1] = fmaf(k4.w, v2.y, U[3][1]);
   }
+  float* dst = before + (static_cast<size_t>(slot) * heads + h) * d * dv;
 #pragma unroll
-  for (int m = 0; m < 4; ++m) {
-    const int i = ti * 32 + ty + 8 * m;
-    if (i < d && col < dv) st[static_cast<size_t>(i) * dv + col] = S[m];
+  for (int m = 0; m < 4; ++m)
+    if (row0 + m < d && col < dv)
+      *reinterpret_cast<float2*>(dst + static_cast<size_t>(row0 + m) * dv + col) = make_float2(U[m][0], U[m][1]);
+}
+
+// (2b) grid (rows, heads, pieces of 256 elements): S = the row's state (zeros at a sequence's start); chunk by
+// chunk, what `before` holds (U) is replaced by S and S becomes decay^L S + U; the last S is the row's new state.
+// One element a thread (many warps an SM) and four chunks' U fetched before the four dependent updates: the walk
+// over a row's chunks is a chain of loads, and only loads in flight hide their latency.
+__global__ void __launch_bounds__(256)
+retention_fold_kernel(float* __restrict__ before, float* __restrict__ state, const float* __restrict__ decay,
+                      const int* __restrict__ cu_q, const int* __restrict__ prefix_len,
+                      const int* __restrict__ state_slots, const int* __restrict__ chunk_base, int heads, int d, int dv) {
+  const int r = blockIdx.x, h = blockIdx.y;
+  const int at = blockIdx.z * blockDim.x + threadIdx.x;
+  const int size = d * dv;
+  if (at >= size) return;
+  const int n = cu_q[r + 1] - cu_q[r];
+  const int chunks = (n + RC - 1) / RC;
+  const float lg = log2f(decay[h]);
+  float* st = state + (static_cast<size_t>(state_slots[r]) * heads + h) * size + at;
+  float S = prefix_len[r] > 0 ? *st : 0.0f;
+  const float whole = exp2f(static_cast<float>(RC) * lg);
+  const float last = n % RC == 0 ? whole : exp2f(static_cast<float>(n % RC) * lg);
+  float* slot = before + (static_cast<size_t>(chunk_base[r]) * heads + h) * size + at;
+  const size_t step = static_cast<size_t>(heads) * size;
+  int c = 0;
+  for (; c + 4 <= chunks; c += 4) {
+    float u[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) u[i] = slot[(c + i) * step];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      slot[(c + i) * step] = S;
+      S = fmaf(c + i == chunks - 1 ? last : whole, S, u[i]);
+    }
   }
+  for (; c < chunks; ++c) {
+    const float u = slot[c * step];
+    slot[c * step] = S;
+    S = fmaf(c == chunks - 1 ? last : whole, S, u);
+  }
+  *st = S;
 }
 
 // acc[TM][TN] += sum over k < K of At[k][row0 + a] * B[k][col0 + b]; At and B in shared memory, k-major, with
@@ -480,9 +492,12 @@ static int launch_chunked(const void* x, int in_stride, float* o, float* state, 
   retention_rotate_kernel<T><<<dim3(tokens, (2 * heads * d + 255) / 256), 256, 0, stream>>>(
       xt, in_stride, qf, kf, inv_freq, rot_dim, k_scale, positions, heads, d);
   retention_chunk_base_kernel<<<1, 32, 0, stream>>>(cu_q, num_rows, chunk_base);
-  const dim3 sgrid(num_rows, heads, ((d + 31) / 32) * ((dv + 31) / 32));
-  retention_state_kernel<T><<<sgrid, 256, 0, stream>>>(xt, in_stride, kf, before, state, decay, cu_q, prefix_len,
-                                                       state_slots, chunk_base, heads, d, dv);
+  const dim3 ugrid(max_chunks, heads, ((d + RS_I - 1) / RS_I) * ((dv + RS_J - 1) / RS_J));
+  retention_chunk_sum_kernel<T><<<ugrid, 256, 0, stream>>>(xt, in_stride, kf, before, decay, cu_q, chunk_base, num_rows,
+                                                           heads, d, dv);
+  const dim3 fgrid(num_rows, heads, (d * dv + 255) / 256);
+  retention_fold_kernel<<<fgrid, 256, 0, stream>>>(before, state, decay, cu_q, prefix_len, state_slots, chunk_base,
+                                                    heads, d, dv);
   const size_t smem = kChunkSmemFloats * sizeof(float);
   static bool configured = false;
   if (!configured) {
