@@ -154,7 +154,9 @@ struct WarpAcc {
 // One block of 32 keys against the 16 query rows in `qs`.  `qpos0/1`: position of the query in rows
 // lane/4 and lane/4 + 8 (-1: the row is unused).  `sf`: scale, soft-cap and the form of the weights (ScoreForm).
 // MASKED = false: the caller knows that every key of the block is visible to every used row of the warp.
-template <bool MASKED>
+// SHAPED: the score may be soft-capped and the weights split in two terms (`sf`); false: the plain form, which
+// carries none of that code.
+template <bool MASKED, bool SHAPED>
 __device__ __forceinline__ void block_mma(const bf16* qs, const unsigned char* ks, const unsigned char* vs, int first_key, int kv_end,
                                           int window, int qpos0, int qpos1, const ScoreForm& sf, WarpAcc& st) {
   const int lane = threadIdx.x & 31;
@@ -188,7 +190,7 @@ __device__ __forceinline__ void block_mma(const bf16* qs, const unsigned char* k
         v1 = in_seq && v1 && key <= qpos1 && (window <= 0 || key > qpos1 - window);
       }
       float a0 = s[n][e] * sf.scale_log2, a1 = s[n][2 + e] * sf.scale_log2;
-      if (sf.cap_log2 > 0.0f) {
+      if (SHAPED && sf.cap_log2 > 0.0f) {
         a0 = sf.cap_log2 * tanh_by_exp2(s[n][e] * sf.tanh_in);
         a1 = sf.cap_log2 * tanh_by_exp2(s[n][2 + e] * sf.tanh_in);
       }
@@ -224,18 +226,25 @@ __device__ __forceinline__ void block_mma(const bf16* qs, const unsigned char* k
   }
 #pragma unroll
   for (int kk = 0; kk < 2; ++kk) {
-    uint32_t a[4], rest[4];
-    a[0] = pack_bf16_rest(s[2 * kk][0], s[2 * kk][1], rest[0]);
-    a[1] = pack_bf16_rest(s[2 * kk][2], s[2 * kk][3], rest[1]);
-    a[2] = pack_bf16_rest(s[2 * kk + 1][0], s[2 * kk + 1][1], rest[2]);
-    a[3] = pack_bf16_rest(s[2 * kk + 1][2], s[2 * kk + 1][3], rest[3]);
+    uint32_t a[4], rest[4] = {0u, 0u, 0u, 0u};
+    if constexpr (SHAPED) {
+      a[0] = pack_bf16_rest(s[2 * kk][0], s[2 * kk][1], rest[0]);
+      a[1] = pack_bf16_rest(s[2 * kk][2], s[2 * kk][3], rest[1]);
+      a[2] = pack_bf16_rest(s[2 * kk + 1][0], s[2 * kk + 1][1], rest[2]);
+      a[3] = pack_bf16_rest(s[2 * kk + 1][2], s[2 * kk + 1][3], rest[3]);
+    } else {
+      a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+      a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+      a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+    }
 #pragma unroll
     for (int dn = 0; dn < D / 8; dn += 2) {
       uint32_t b[4];
       ldmatrix_x4_trans(b, vs + swz(kk * 16 + (mi & 1) * 8 + r8, dn + (mi >> 1)));
       mma_bf16(st.o[dn], a, b[0], b[1]);
       mma_bf16(st.o[dn + 1], a, b[2], b[3]);
-      if (sf.split_p) {
+      if (SHAPED && sf.split_p) {
         mma_bf16(st.o[dn], rest, b[0], b[1]);
         mma_bf16(st.o[dn + 1], rest, b[2], b[3]);
       }
@@ -247,7 +256,7 @@ __device__ __forceinline__ void block_mma(const bf16* qs, const unsigned char* k
 // grid (splits, nkv, decode rows).  Partials: part_acc[((row * nh + head) * splits + split) * D + dim]
 // (unnormalised), part_ml[...][2] = (maximum in log2 units, sum).
 // Shared memory: [WARPS][STAGES] tiles (1024-byte aligned), the query tile [16][LD], the barriers.
-template <int WARPS, int STAGES>
+template <int WARPS, int STAGES, bool SHAPED>
 __global__ void __launch_bounds__(WARPS * 32, 1)
 decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                   const bf16* __restrict__ q, bf16* __restrict__ out, float* __restrict__ part_acc,
@@ -341,9 +350,9 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     }
     __syncwarp();
     if (first_key + KB <= kv_end && (window <= 0 || first_key > qp - window))
-      block_mma<false>(qs, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos0, qpos1, sf, st);
+      block_mma<false, SHAPED>(qs, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos0, qpos1, sf, st);
     else
-      block_mma<true>(qs, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos0, qpos1, sf, st);
+      block_mma<true, SHAPED>(qs, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos0, qpos1, sf, st);
     __syncwarp();                                      // every lane is done reading before the stage is refilled
     if (++stage == STAGES) { stage = 0; parity ^= 1u; }
   }
@@ -461,7 +470,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 
-template <int STAGES>
+template <int STAGES, bool SHAPED>
 __global__ void __launch_bounds__(PF_WARPS * 32, PF_MIN_CTAS)
 prefill_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                    const bf16* __restrict__ q, bf16* __restrict__ out, const int* __restrict__ block_table,
@@ -571,9 +580,9 @@ prefill_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
       const bool all_visible = first_key + KB - 1 <= p_lo + w_tok_lo && first_key + KB <= kv_end &&
                                (window <= 0 || first_key > w_p_hi - window);
       if (all_visible)
-        block_mma<false>(my_q, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos[0], qpos[1], sf, st);
+        block_mma<false, SHAPED>(my_q, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos[0], qpos[1], sf, st);
       else
-        block_mma<true>(my_q, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos[0], qpos[1], sf, st);
+        block_mma<true, SHAPED>(my_q, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos[0], qpos[1], sf, st);
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(empty + s);
@@ -668,12 +677,13 @@ B200_EXPORT int b200_decode_attention_mma(const void* q, const void* k_map, cons
   if ((page_size & (page_size - 1)) != 0) return B200_BAD_SIZE;
   const int box_rows = page_size < KB ? page_size : KB;
   constexpr size_t smem = kFixedBytes + static_cast<size_t>(kWarps) * kStages * TILE_BYTES;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<kWarps, kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(smem));
+  const bool shaped = softcap > 0.0f || split_p != 0;
+  auto* kernel = shaped ? decode_mma_kernel<kWarps, kStages, true> : decode_mma_kernel<kWarps, kStages, false>;
+  static bool configured[2] = {false, false};
+  if (!configured[shaped]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
+    configured[shaped] = true;
   }
   CUtensorMap kmap, vmap;
   memcpy(&kmap, k_map, sizeof(kmap));
@@ -695,7 +705,7 @@ B200_EXPORT int b200_decode_attention_mma(const void* q, const void* k_map, cons
   }
   const bool cluster_merge = (splits == 2 || splits == 4 || splits == 8) &&
                              static_cast<long long>(splits) * nkv * n_rows <= sm_count;
-  int rc = b200_launch(decode_mma_kernel<kWarps, kStages>, grid, dim3(kWarps * 32), smem, stream, cluster_merge ? splits : 0,
+  int rc = b200_launch(kernel, grid, dim3(kWarps * 32), smem, stream, cluster_merge ? splits : 0,
                        kmap, vmap, static_cast<const bf16*>(q), static_cast<bf16*>(out), part_acc, part_ml, block_table,
                        table_stride, cu_q, kv_len, rows, nh, nkv, page_size, box_rows, window,
                        score_form(scale, softcap, split_p), cluster_merge ? 1 : 0, err);
@@ -723,12 +733,13 @@ B200_EXPORT int b200_prefill_attention_mma(const void* q, const void* k_map, con
   const int box_rows = page_size < KB ? page_size : KB;
   const int tile_tokens = (16 / (nh / nkv)) * PF_WARPS;
   constexpr size_t smem = kPfFixed + static_cast<size_t>(kPfStages) * TILE_BYTES;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(prefill_mma_kernel<kPfStages>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(smem));
+  const bool shaped = softcap > 0.0f || split_p != 0;
+  auto* kernel = shaped ? prefill_mma_kernel<kPfStages, true> : prefill_mma_kernel<kPfStages, false>;
+  static bool configured[2] = {false, false};
+  if (!configured[shaped]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
+    configured[shaped] = true;
   }
   CUtensorMap kmap, vmap;
   memcpy(&kmap, k_map, sizeof(kmap));
@@ -736,7 +747,7 @@ B200_EXPORT int b200_prefill_attention_mma(const void* q, const void* k_map, con
   const int n_tiles = (max_q_len + tile_tokens - 1) / tile_tokens;
   if (n_rows > 65535 || n_tiles > 65535) return B200_BAD_SIZE;      // the grid's y and z extents
   dim3 grid(nkv, n_rows, n_tiles);
-  prefill_mma_kernel<kPfStages><<<grid, PF_WARPS * 32, smem, stream>>>(
+  kernel<<<grid, PF_WARPS * 32, smem, stream>>>(
       kmap, vmap, static_cast<const bf16*>(q), static_cast<bf16*>(out), block_table, table_stride, cu_q, kv_len,
       prefix_len, rows, nh, nkv, page_size, box_rows, window, score_form(scale, softcap, split_p), err);
   return b200_check_launch();
