@@ -76,6 +76,12 @@ CONFIGS["K4"] = config(61, 24, 1e-5, [
     retention(2, 8, 8, [0.9, 0.8]),
 ], canon_taps=1)
 
+# heads wider than 128: the all-sizes attention kernel with keys of 160 and values of 136, retention by the scan alone
+CONFIGS["K5"] = config(73, 56, 1e-5, [
+    attention(2, 1, 160, 136, 0.08, conv=2, rot={"base": 1000.0, "dims": 96}, softcap=10.0, ff=48),
+    retention(1, 192, 72, [0.99], rot={"base": 1000.0, "dims": 64}),
+], canon_taps=2)
+
 # One mixer alone, the attention one with scores so sharp that a single key decides a position's result; widths
 # that are no whole 16-byte pieces (the kernels' one-channel-a-thread forms).
 ONLY_ATTENTION = config(89, 34, 1e-5, [
@@ -173,6 +179,14 @@ def run_alone(engine, rid: int, ids: Sequence[int], portions: Sequence[int]) -> 
 
 
 TOL = {"float32": 2e-5, "bfloat16": 4e-2}
+# The one-mixer attention model has scores up to its cap of 30: q and k rounded to bfloat16 (2^-9 each) move such a
+# score by up to 30 * 2^-8 = 0.12, and so a key's weight by 12 %.  Its bfloat16 bound is that share of the logits' scale;
+# its float32 bound is the common one, and that is the run which shows a wrong key.
+SHARP_BF16_TOL = 0.12
+
+
+def tolerance(name: str, dtype: str) -> float:
+    return SHARP_BF16_TOL if (name == "attention" and dtype == "bfloat16") else TOL[dtype]
 
 
 def check(got: np.ndarray, want: np.ndarray, dtype: str, what: str, tol: float = None) -> None:

@@ -154,7 +154,7 @@ def test_poly_norm_and_gates(dtype, width):
 
 
 @pytest.mark.parametrize("chunked", [False, True])
-@pytest.mark.parametrize("heads,d,dv,rot", [(2, 8, 16, 4), (1, 24, 40, 24), (3, 100, 36, 0), (2, 128, 128, 64)])
+@pytest.mark.parametrize("heads,d,dv,rot", [(2, 8, 16, 4), (1, 24, 40, 24), (3, 100, 36, 0), (2, 128, 128, 64), (1, 320, 72, 32)])
 def test_retention_kernel_against_the_recurrence_in_portions(heads, d, dv, rot, chunked):
     from llm_infer_rust_b200.kernels import ops
     dev = torch.device("cuda")
@@ -226,17 +226,18 @@ def cut(total, pattern):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["K1", "K2", "K3", "K4", "attention", "retention"])
+@pytest.mark.parametrize("name", ["K1", "K2", "K3", "K4", "K5", "attention", "retention"])
 def test_whole_decoded_and_in_portions(name, dtype, models):
     raw, w, folder = models[name]
     T = 150
     ids = K.tokens(raw["vocab"], T, 3)
     want = K.oracle(raw, w, ids)
     eng = K.make_engine(folder, dtype, page_size=8, pool_tokens=256)
-    K.check(K.run_alone(eng, 1, ids, [T]), want, dtype, "whole")
-    K.check(K.run_alone(eng, 2, ids, [T - 40] + [1] * 40), want, dtype, "last 40 decoded")
-    K.check(K.run_alone(eng, 3, ids, cut(T, PORTIONS)), want, dtype, "in portions")
-    K.check(K.run_alone(eng, 4, ids[:24], [1] * 24), want[:24], dtype, "token by token from the first")
+    tol = K.tolerance(name, dtype)
+    K.check(K.run_alone(eng, 1, ids, [T]), want, dtype, "whole", tol)
+    K.check(K.run_alone(eng, 2, ids, [T - 40] + [1] * 40), want, dtype, "last 40 decoded", tol)
+    K.check(K.run_alone(eng, 3, ids, cut(T, PORTIONS)), want, dtype, "in portions", tol)
+    K.check(K.run_alone(eng, 4, ids[:24], [1] * 24), want[:24], dtype, "token by token from the first", tol)
     assert eng.cache.manager.check() == ""
 
 
@@ -250,9 +251,10 @@ def test_far_keys_with_sharp_scores_and_slow_decays(dtype, models):
         ids = K.tokens(raw["vocab"], T, 11)
         want = K.oracle(raw, w, ids)
         eng = K.make_engine(folder, dtype, page_size=16, pool_tokens=768)
-        K.check(K.run_alone(eng, 1, ids, [T]), want, dtype, name + " whole")
-        K.check(K.run_alone(eng, 2, ids, [T - 70, 37, 2] + [1] * 31), want, dtype, name + " tail decoded")
-        K.check(K.run_alone(eng, 3, ids, cut(T, [127, 2, 16, 129, 15, 1 + 16 * 7])), want, dtype, name + " in portions")
+        tol = K.tolerance(name, dtype)
+        K.check(K.run_alone(eng, 1, ids, [T]), want, dtype, name + " whole", tol)
+        K.check(K.run_alone(eng, 2, ids, [T - 70, 37, 2] + [1] * 31), want, dtype, name + " tail decoded", tol)
+        K.check(K.run_alone(eng, 3, ids, cut(T, [127, 2, 16, 129, 15, 1 + 16 * 7])), want, dtype, name + " in portions", tol)
         del eng
 
 
