@@ -310,16 +310,19 @@ def test_long_decoding(dtype, models):
     K.check(K.run_alone(eng, 1, ids, [6] + [1] * 254), K.oracle(raw, w, ids), dtype, "254 tokens decoded one by one")
 
 
-@pytest.mark.parametrize("dtype,graphs", [("float32", 0), ("bfloat16", 0), ("bfloat16", 4)])
-def test_greedy_generation_through_the_scheduler(dtype, graphs, models):
+@pytest.mark.parametrize("dtype,graphs,portion_graphs", [("float32", 0, 0), ("bfloat16", 0, 0), ("bfloat16", 4, 0),
+                                                         ("bfloat16", 4, 64)])
+def test_greedy_generation_through_the_scheduler(dtype, graphs, portion_graphs, models):
     """``Engine.generate``: prompts cut by the scheduler's token budget, more prompts than state slots, decode
-    graphs in bfloat16.  float32: the tokens are the plain implementation's; bfloat16: every generated token
-    is one whose plain logit is within a small margin of the best."""
+    graphs in bfloat16, and graphs of prompt portions whose shape comes again (captured on throw-away requests
+    while live requests hold states).  float32: the tokens are the plain implementation's; bfloat16: every
+    generated token is one whose plain logit is within a small margin of the best."""
     from llm_infer_rust_b200 import SamplingParams
     raw, w, folder = models["K3"]
-    prompts = [K.tokens(raw["vocab"], n, 40 + n) for n in (5, 23, 1, 12, 30)]
+    prompts = [K.tokens(raw["vocab"], n, 40 + n) for n in (5, 23, 1, 12, 30, 64, 50)]
     eng = K.make_engine(folder, dtype, page_size=8, pool_tokens=512, max_requests=3, cuda_graph_bs=graphs,
-                        chunked_prefill_size=16, max_prefill_tokens_per_batch=16)
+                        chunked_prefill_size=16, max_prefill_tokens_per_batch=16,
+                        prefill_cuda_graph_max_tokens=portion_graphs)
     results = eng.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
     eng.check_kernel_errors()
     for prompt, res in zip(prompts, results):
