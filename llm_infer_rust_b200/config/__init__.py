@@ -3,7 +3,8 @@ from .registry import (Architecture, register_architecture, registered_architect
                        resolve_architecture)
 from .qwen3 import Qwen3Config
 from .kefetar import KefetarConfig
+from .mukenex import MukenexConfig
 
 __all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "RunEntry", "Architecture",
            "register_architecture", "registered_architectures", "resolve_architecture",
-           "Qwen3Config", "KefetarConfig"]
+           "Qwen3Config", "KefetarConfig", "MukenexConfig"]

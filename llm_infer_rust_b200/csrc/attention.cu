@@ -9,6 +9,10 @@
 // in shared memory HEAD_DIM wide with zeros beyond `hd`.  Values may have a width of their own (`hd_v`, rows of
 // the value cache and of the output; HEAD_DIM covers the wider of the two), and a score may be soft-capped:
 // s <- cap * tanh(s / cap) after the scale and before the mask (cap <= 0: no cap).
+// Two more masks and a term of the denominator, each off unless asked for: `chunk` C > 0 lets the query at position p
+// see key j only if j >= p - p % C (keys of the query's own block of C positions, blocks counted from position 0 of
+// the sequence); `sinks` (one float per query head) adds exp(sink_h) to the softmax's denominator: a term without a
+// key and without a value, not scaled.
 //
 // Semantics (reference: src/models/attention/backend.rs:1455-1498): query head h
 // reads KV head h / (nh / nkv); score = q.k / sqrt(d) (the scale is a
@@ -72,7 +76,7 @@ struct VecState {
 //  ps     : shared memory, 32 * NV floats private to the warp
 template <typename T>
 __device__ __forceinline__ void warp_key_block(const T* ks, const T* vs, const float* qs, const int* qpos,
-                                               int first_key, int kv_end, int window, VecState& st,
+                                               int first_key, int kv_end, int window, int chunk, VecState& st,
                                                float* ps, float softcap) {
   using G = RowGeom<T>;
   const int lane = threadIdx.x & 31;
@@ -106,7 +110,8 @@ __device__ __forceinline__ void warp_key_block(const T* ks, const T* vs, const f
 #pragma unroll
   for (int v = 0; v < NV; ++v) {
     const int p = qpos[v];
-    const bool visible = p >= 0 && key <= p && key < kv_end && (window <= 0 || key > p - window);
+    const bool visible = p >= 0 && key <= p && key < kv_end && (window <= 0 || key > p - window) &&
+                         (chunk <= 0 || key >= p - p % chunk);
     const float sv = visible ? s[v] : -INFINITY;
     const float m_new = fmaxf(st.m[v], warp_max(sv));
     float prob = 0.0f, corr = 1.0f;
@@ -194,7 +199,7 @@ prefill_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
                          const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                          const int* __restrict__ prefix_len, const int* __restrict__ rows, int nh, int nkv,
                          int page_size, int window, float scale, int tile_tokens, int head_chunks, int hd,
-                         int hd_v, float softcap) {
+                         int hd_v, float softcap, int chunk, const float* __restrict__ sinks) {
   using G = RowGeom<T>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* qs = reinterpret_cast<float*>(smem_raw);                        // [32][D]
@@ -215,6 +220,7 @@ prefill_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
   const int kv_end = min(kv_len[row], prefix + tok0 + ntok);            // causal: nothing later is visible
   const int p_lo = prefix + tok0;
   int k_begin = window > 0 ? max(0, p_lo - window + 1) : 0;
+  if (chunk > 0) k_begin = max(k_begin, p_lo - p_lo % chunk);      // the tile's first query sees the earliest block
   k_begin -= k_begin % KB;
   const int* table = block_table + static_cast<size_t>(row) * table_stride;
 
@@ -245,9 +251,10 @@ prefill_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
-    const bool touches = warp_p_max >= kb && (window <= 0 || kb + KB - 1 > warp_p_min - window);
+    const bool touches = warp_p_max >= kb && (window <= 0 || kb + KB - 1 > warp_p_min - window) &&
+                         (chunk <= 0 || kb + KB - 1 >= warp_p_min - warp_p_min % chunk);
     if (touches)
-      warp_key_block<T>(ks, vs, qs + warp * NV * D, qpos, kb, kv_end, window, st, ps + warp * KB * NV, softcap);
+      warp_key_block<T>(ks, vs, qs + warp * NV * D, qpos, kb, kv_end, window, chunk, st, ps + warp * KB * NV, softcap);
   }
 #pragma unroll
   for (int v = 0; v < NV; ++v) {
@@ -255,7 +262,9 @@ prefill_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
     if (vec >= nvec) continue;
     const int tok = vec / group, head = head_base + vec % group;
     T* dst = out + (static_cast<size_t>(q_begin + tok0 + tok) * nh + head) * hd_v;
-    const float inv = st.l[v] > 0.0f ? 1.0f / st.l[v] : 0.0f;
+    float l = st.l[v];
+    if (sinks != nullptr && l > 0.0f) l += expf(sinks[head] - st.m[v]);
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
 #pragma unroll
     for (int k = 0; k < PAIRS; ++k) {
       const int dim = 2 * lane + 64 * k;
@@ -281,7 +290,7 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
                         const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_q,
                         const int* __restrict__ kv_len, const int* __restrict__ rows, int nh, int nkv,
                         int page_size, int window, float scale, int vec_groups, int stages, int hd, int hd_v,
-                        float softcap) {
+                        float softcap, int chunk, const float* __restrict__ sinks) {
   using G = RowGeom<T>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* qs = reinterpret_cast<float*>(smem_raw);                        // [NV][D]
@@ -298,6 +307,7 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
   const int kv_end = kv_len[row];
   const int qp = kv_end - 1;                                             // the decoded token's position
   int k_begin = window > 0 ? max(0, qp - window + 1) : 0;
+  if (chunk > 0) k_begin = max(k_begin, qp - qp % chunk);
   k_begin -= k_begin % KB;
   const int blocks_total = (kv_end - k_begin + KB - 1) / KB;
   const int per_split = (blocks_total + splits - 1) / splits;
@@ -350,7 +360,7 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
     }
     __syncwarp();
     const T* t = my_tiles + stage * tile_elems;
-    warp_key_block<T>(t, t + KB * G::STRIDE, qs, qpos, k_begin + blk * KB, kv_end, window, st,
+    warp_key_block<T>(t, t + KB * G::STRIDE, qs, qpos, k_begin + blk * KB, kv_end, window, chunk, st,
                       ps + warp * KB * NV, softcap);
     stage = (stage + 1) % stages;
   }
@@ -387,6 +397,7 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
     }
     const int head = head0 + v;
     if (splits == 1) {
+      if (sinks != nullptr && l > 0.0f) l += expf(sinks[head] - m);
       if (dim < hd_v) out[(static_cast<size_t>(tok) * nh + head) * hd_v + dim] = from_f32<T>(l > 0.0f ? o / l : 0.0f);
     } else {
       const size_t slot = (static_cast<size_t>(blockIdx.z) * nh + head) * splits + split;
@@ -400,7 +411,8 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
 template <typename T>
 __global__ void decode_merge_kernel(T* __restrict__ out, const float* __restrict__ part_acc,
                                     const float* __restrict__ part_ml, const int* __restrict__ cu_q,
-                                    const int* __restrict__ rows, int nh, int splits, int hd) {
+                                    const int* __restrict__ rows, int nh, int splits, int hd,
+                                    const float* __restrict__ sinks) {
   const int head = blockIdx.y;
   const int tok = cu_q[rows[blockIdx.x]];
   const size_t base = (static_cast<size_t>(blockIdx.x) * nh + head) * splits;
@@ -414,6 +426,7 @@ __global__ void decode_merge_kernel(T* __restrict__ out, const float* __restrict
         l += part_ml[(base + s) * 2 + 1] * f;
         o += part_acc[(base + s) * D + dim] * f;
       }
+      if (sinks != nullptr && l > 0.0f) l += expf(sinks[head] - m);
     }
     out[(static_cast<size_t>(tok) * nh + head) * hd + dim] = from_f32<T>(l > 0.0f ? o / l : 0.0f);
   }
@@ -424,7 +437,8 @@ template <typename T>
 static int launch_prefill(const void* q, const void* kc, const void* vc, void* out, const int* block_table,
                           int table_stride, const int* cu_q, const int* kv_len, const int* prefix_len,
                           const int* rows, int n_rows, int max_q_len, int nh, int nkv, int page_size, int window,
-                          float scale, int hd, int hd_v, float softcap, cudaStream_t stream) {
+                          float scale, int hd, int hd_v, float softcap, int chunk, const float* sinks,
+                          cudaStream_t stream) {
   using G = RowGeom<T>;
   const int group = nh / nkv;
   const int head_chunks = (group + 31) / 32;                  // more than 32 query heads per KV head: several CTAs
@@ -442,7 +456,7 @@ static int launch_prefill(const void* q, const void* kc, const void* vc, void* o
   prefill_attention_kernel<T><<<grid, PF_WARPS * 32, smem, stream>>>(
       static_cast<const T*>(q), static_cast<const T*>(kc), static_cast<const T*>(vc), static_cast<T*>(out),
       block_table, table_stride, cu_q, kv_len, prefix_len, rows, nh, nkv, page_size, window, scale, tile_tokens,
-      head_chunks, hd, hd_v, softcap);
+      head_chunks, hd, hd_v, softcap, chunk, sinks);
   return b200_check_launch();
 }
 
@@ -450,7 +464,8 @@ template <typename T>
 static int launch_decode(const void* q, const void* kc, const void* vc, void* out, float* part_acc, float* part_ml,
                          const int* block_table, int table_stride, const int* cu_q, const int* kv_len,
                          const int* rows, int n_rows, int nh, int nkv, int page_size, int window, float scale,
-                         int splits, int hd, int hd_v, float softcap, cudaStream_t stream) {
+                         int splits, int hd, int hd_v, float softcap, int chunk, const float* sinks,
+                         cudaStream_t stream) {
   using G = RowGeom<T>;
   const int group = nh / nkv;
   const int vec_groups = (group + NV - 1) / NV;
@@ -476,12 +491,12 @@ static int launch_decode(const void* q, const void* kc, const void* vc, void* ou
   decode_attention_kernel<T, DEC_WARPS><<<grid, DEC_WARPS * 32, smem, stream>>>(
       static_cast<const T*>(q), static_cast<const T*>(kc), static_cast<const T*>(vc), static_cast<T*>(out),
       part_acc, part_ml, block_table, table_stride, cu_q, kv_len, rows, nh, nkv, page_size, window, scale,
-      vec_groups, stages, hd, hd_v, softcap);
+      vec_groups, stages, hd, hd_v, softcap, chunk, sinks);
   int rc = b200_check_launch();
   if (rc != 0 || splits == 1) return rc;
   dim3 mgrid(n_rows, nh);
   decode_merge_kernel<T><<<mgrid, D >= 128 ? 128 : 64, 0, stream>>>(static_cast<T*>(out), part_acc, part_ml, cu_q,
-                                                                   rows, nh, splits, hd_v);
+                                                                   rows, nh, splits, hd_v, sinks);
   return b200_check_launch();
 }
 
@@ -492,7 +507,8 @@ B200_EXPORT int b200_prefill_attention(const void* q, const void* k_cache, const
                                        const int* block_table, int table_stride, const int* cu_q,
                                        const int* kv_len, const int* prefix_len, const int* rows, int n_rows,
                                        int max_q_len, int nh, int nkv, int page_size, int window, float scale,
-                                       int dtype, int head_dim, int v_head_dim, float softcap, cudaStream_t stream) {
+                                       int dtype, int head_dim, int v_head_dim, float softcap, int chunk,
+                                       const float* sinks, cudaStream_t stream) {
   if (n_rows <= 0 || max_q_len <= 0) return 0;
   if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0) return B200_BAD_SIZE;
   if (head_dim <= 0 || head_dim > D || (head_dim & 1)) return B200_BAD_SIZE;
@@ -500,11 +516,11 @@ B200_EXPORT int b200_prefill_attention(const void* q, const void* k_cache, const
   if (dtype == B200_F32)
     return launch_prefill<float>(q, k_cache, v_cache, out, block_table, table_stride, cu_q, kv_len, prefix_len,
                                  rows, n_rows, max_q_len, nh, nkv, page_size, window, scale, head_dim, v_head_dim,
-                                 softcap, stream);
+                                 softcap, chunk, sinks, stream);
   if (dtype == B200_BF16)
     return launch_prefill<__nv_bfloat16>(q, k_cache, v_cache, out, block_table, table_stride, cu_q, kv_len,
                                          prefix_len, rows, n_rows, max_q_len, nh, nkv, page_size, window, scale,
-                                         head_dim, v_head_dim, softcap, stream);
+                                         head_dim, v_head_dim, softcap, chunk, sinks, stream);
   return B200_BAD_DTYPE;
 }
 
@@ -519,7 +535,8 @@ B200_EXPORT int b200_decode_attention(const void* q, const void* k_cache, const 
                                       float* scratch, const int* block_table, int table_stride,
                                       const int* cu_q, const int* kv_len, const int* rows, int n_rows, int nh,
                                       int nkv, int page_size, int window, float scale, int splits, int dtype,
-                                      int head_dim, int v_head_dim, float softcap, cudaStream_t stream) {
+                                      int head_dim, int v_head_dim, float softcap, int chunk, const float* sinks,
+                                      cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || splits <= 0) return B200_BAD_SIZE;
   if (head_dim <= 0 || head_dim > D || (head_dim & 1)) return B200_BAD_SIZE;
@@ -529,10 +546,10 @@ B200_EXPORT int b200_decode_attention(const void* q, const void* k_cache, const 
   if (dtype == B200_F32)
     return launch_decode<float>(q, k_cache, v_cache, out, part_acc, part_ml, block_table, table_stride, cu_q,
                                 kv_len, rows, n_rows, nh, nkv, page_size, window, scale, splits, head_dim, v_head_dim,
-                                softcap, stream);
+                                softcap, chunk, sinks, stream);
   if (dtype == B200_BF16)
     return launch_decode<__nv_bfloat16>(q, k_cache, v_cache, out, part_acc, part_ml, block_table, table_stride,
                                         cu_q, kv_len, rows, n_rows, nh, nkv, page_size, window, scale, splits,
-                                        head_dim, v_head_dim, softcap, stream);
+                                        head_dim, v_head_dim, softcap, chunk, sinks, stream);
   return B200_BAD_DTYPE;
 }

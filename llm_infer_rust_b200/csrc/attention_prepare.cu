@@ -1,0 +1,209 @@
+// What stands between a packed projection and attention, for two kinds of mixer.  One warp owns one vector of a
+// token; values are read once, worked on in float in shared memory and rounded once when stored.
+//
+// (1) heads_prepare: grouped-query attention whose keys are `d` wide and whose values are `dv` wide.  The packed
+//     row holds q (nh * d), k (nkv * d), v (nkv * dv) from column 0.  Optional, in this order: a bias per column;
+//     a per-head RMS norm of q and of k (x / sqrt(mean(x^2) + eps) * w, one weight vector for all heads);
+//     a rotation of the first rot_dims coordinates of every q and k head.  q goes to q_out [tokens, nh * d], k and
+//     v to the paged cache at the token's slot.
+//
+// (2) latent_prepare: attention over a narrow latent.  The packed row holds per head [d plain | r rotated] query
+//     coordinates (nh * (d + r)), then the down projection [c_dim latent | r rotated key part].  The latent is
+//     RMS-normed (weight w_c) and, with the rotated key part behind it, is the ONE key of the token
+//     (c_dim + r wide, shared by all heads); the latent alone is its value.  The query against that key is
+//     [q_lat (c_dim) | rotated (r)], where q_lat[h] = W_uk[h]^T q_plain[h] was multiplied before
+//     (q_lat: [nh, tokens, c_dim]), since q_plain . (W_uk[h] c) = (W_uk[h]^T q_plain) . c.
+//
+// Rotation: the pair (u, v) of a token at position p becomes (u cos a - v sin a, v cos a + u sin a) with
+// a = p * inv_freq[i] in float; pairs are (2i, 2i + 1) (`interleaved`) or (i, i + rot_dims / 2).
+// A slot outside the pool sets an error bit and the store is skipped; slot 0 (padding rows) stores nothing.
+#include "common.cuh"
+
+constexpr int MAX_VEC = 1024;       // widest vector a warp takes
+constexpr int WARPS = 4;
+
+__device__ __forceinline__ void rotate_row(float* row, int rot_dims, float pos, const float* __restrict__ inv_freq,
+                                           bool interleaved, int lane) {
+  const int half = rot_dims >> 1;
+  for (int i = lane; i < half; i += 32) {
+    const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+    float sn, cs;
+    sincosf(pos * inv_freq[i], &sn, &cs);
+    const float u = row[a], v = row[b];
+    row[a] = u * cs - v * sn;
+    row[b] = v * cs + u * sn;
+  }
+}
+
+// cache[page][kv head][offset in page][width]: the row of `slot` for KV head kvh, or null (with the error bit set
+// for a slot outside the pool)
+template <typename T>
+__device__ __forceinline__ T* cache_row(T* cache, int slot, int kvh, int nkv, int page_size, long long cache_slots,
+                                        int width, int lane, int* err) {
+  if (slot == 0) return nullptr;
+  if (slot < 0 || slot >= cache_slots) {
+    if (lane == 0) atomicOr(err, B200_ERR_SLOT_RANGE);
+    return nullptr;
+  }
+  const int page = slot / page_size, offset = slot - page * page_size;
+  return cache + ((static_cast<size_t>(page) * nkv + kvh) * page_size + offset) * width;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(WARPS * 32)
+heads_prepare_kernel(const T* __restrict__ x, int in_stride, const float* __restrict__ bias,
+                     const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                     const float* __restrict__ inv_freq, int rot_dims, int interleaved,
+                     const int* __restrict__ positions, const int* __restrict__ slots, int tokens, int nh, int nkv,
+                     int d, int dv, int page_size, long long cache_slots, T* __restrict__ q_out,
+                     T* __restrict__ k_cache, T* __restrict__ v_cache, int* err) {
+  __shared__ float buf[WARPS][MAX_VEC];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int vectors = nh + 2 * nkv;
+  const long long work = static_cast<long long>(blockIdx.x) * WARPS + warp;
+  if (work >= static_cast<long long>(tokens) * vectors) return;
+  const int t = static_cast<int>(work / vectors);
+  const int h = static_cast<int>(work - static_cast<long long>(t) * vectors);
+  const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
+  const int kvh = is_q ? 0 : (is_k ? h - nh : h - nh - nkv);
+  const int width = (is_q || is_k) ? d : dv;
+  const int col = is_q ? h * d : (is_k ? nh * d + kvh * d : (nh + nkv) * d + kvh * dv);
+  T* dst;
+  if (is_q) {
+    dst = q_out + (static_cast<size_t>(t) * nh + h) * d;
+  } else {
+    if (slots == nullptr) return;
+    dst = cache_row(is_k ? k_cache : v_cache, slots[t], kvh, nkv, page_size, cache_slots, width, lane, err);
+    if (dst == nullptr) return;
+  }
+  const T* src = x + static_cast<size_t>(t) * in_stride + col;
+  float* row = buf[warp];
+  float ss = 0.0f;
+  for (int i = lane; i < width; i += 32) {
+    float v = to_f32<T>(src[i]);
+    if (bias != nullptr) v += bias[col + i];
+    row[i] = v;
+    ss = fmaf(v, v, ss);
+  }
+  const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
+  if (w != nullptr) {
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss / static_cast<float>(width) + eps);
+    for (int i = lane; i < width; i += 32) row[i] = row[i] * r * w[i];
+  }
+  __syncwarp();
+  if ((is_q || is_k) && inv_freq != nullptr && rot_dims > 0) {
+    rotate_row(row, rot_dims, static_cast<float>(positions[t]), inv_freq, interleaved != 0, lane);
+    __syncwarp();
+  }
+  for (int i = lane; i < width; i += 32) dst[i] = from_f32<T>(row[i]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(WARPS * 32)
+latent_prepare_kernel(const T* __restrict__ x, int in_stride, const T* __restrict__ q_lat,
+                      const float* __restrict__ w_c, float eps, const float* __restrict__ inv_freq, int rot_dims,
+                      int interleaved, const int* __restrict__ positions, const int* __restrict__ slots, int tokens,
+                      int nh, int d, int r, int c_dim, int page_size, long long cache_slots, T* __restrict__ q_out,
+                      T* __restrict__ k_cache, T* __restrict__ v_cache, int* err) {
+  __shared__ float buf[WARPS][MAX_VEC];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int vectors = nh + 1;
+  const long long work = static_cast<long long>(blockIdx.x) * WARPS + warp;
+  if (work >= static_cast<long long>(tokens) * vectors) return;
+  const int t = static_cast<int>(work / vectors);
+  const int h = static_cast<int>(work - static_cast<long long>(t) * vectors);
+  const float pos = static_cast<float>(positions[t]);
+  float* row = buf[warp];
+  if (h < nh) {
+    // a query head: its latent part was multiplied before; its rotated part is turned here
+    const T* src = x + static_cast<size_t>(t) * in_stride + static_cast<size_t>(h) * (d + r) + d;
+    for (int i = lane; i < r; i += 32) row[i] = to_f32<T>(src[i]);
+    __syncwarp();
+    if (inv_freq != nullptr && rot_dims > 0) {
+      rotate_row(row, rot_dims, pos, inv_freq, interleaved != 0, lane);
+      __syncwarp();
+    }
+    T* dst = q_out + (static_cast<size_t>(t) * nh + h) * (c_dim + r);
+    const T* lat = q_lat + (static_cast<size_t>(h) * tokens + t) * c_dim;
+    for (int i = lane; i < c_dim; i += 32) dst[i] = lat[i];
+    for (int i = lane; i < r; i += 32) dst[c_dim + i] = from_f32<T>(row[i]);
+    return;
+  }
+  // the down projection: the normed latent and the rotated key part that all heads share
+  if (slots == nullptr) return;
+  const T* src = x + static_cast<size_t>(t) * in_stride + static_cast<size_t>(nh) * (d + r);
+  float ss = 0.0f;
+  for (int i = lane; i < c_dim + r; i += 32) {
+    const float v = to_f32<T>(src[i]);
+    row[i] = v;
+    if (i < c_dim) ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  const float rs = 1.0f / sqrtf(ss / static_cast<float>(c_dim) + eps);
+  for (int i = lane; i < c_dim; i += 32) row[i] = row[i] * rs * w_c[i];
+  __syncwarp();
+  if (inv_freq != nullptr && rot_dims > 0) {
+    rotate_row(row + c_dim, rot_dims, pos, inv_freq, interleaved != 0, lane);
+    __syncwarp();
+  }
+  const int slot = slots[t];
+  T* kd = cache_row(k_cache, slot, 0, 1, page_size, cache_slots, c_dim + r, lane, err);
+  if (kd == nullptr) return;
+  T* vd = cache_row(v_cache, slot, 0, 1, page_size, cache_slots, c_dim, lane, err);
+  for (int i = lane; i < c_dim + r; i += 32) kd[i] = from_f32<T>(row[i]);
+  for (int i = lane; i < c_dim; i += 32) vd[i] = from_f32<T>(row[i]);
+}
+
+B200_EXPORT int b200_heads_prepare(const void* x, int dtype, int in_stride, const float* bias, const float* q_w,
+                                   const float* k_w, float eps, const float* inv_freq, int rot_dims, int interleaved,
+                                   const int* positions, const int* slots, int tokens, int nh, int nkv, int d, int dv,
+                                   int page_size, long long cache_slots, void* q_out, void* k_cache, void* v_cache,
+                                   int* err, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (nh <= 0 || nkv <= 0 || d <= 0 || dv <= 0 || d > MAX_VEC || dv > MAX_VEC || rot_dims < 0 || rot_dims > d ||
+      (rot_dims & 1) || page_size <= 0)
+    return B200_BAD_SIZE;
+  const long long work = static_cast<long long>(tokens) * (nh + 2 * nkv);
+  const unsigned blocks = static_cast<unsigned>((work + WARPS - 1) / WARPS);
+  if (dtype == B200_F32)
+    heads_prepare_kernel<float><<<blocks, WARPS * 32, 0, stream>>>(
+        static_cast<const float*>(x), in_stride, bias, q_w, k_w, eps, inv_freq, rot_dims, interleaved, positions, slots,
+        tokens, nh, nkv, d, dv, page_size, cache_slots, static_cast<float*>(q_out), static_cast<float*>(k_cache),
+        static_cast<float*>(v_cache), err);
+  else if (dtype == B200_BF16)
+    heads_prepare_kernel<__nv_bfloat16><<<blocks, WARPS * 32, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(x), in_stride, bias, q_w, k_w, eps, inv_freq, rot_dims, interleaved,
+        positions, slots, tokens, nh, nkv, d, dv, page_size, cache_slots, static_cast<__nv_bfloat16*>(q_out),
+        static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), err);
+  else
+    return B200_BAD_DTYPE;
+  return b200_check_launch();
+}
+
+B200_EXPORT int b200_latent_prepare(const void* x, int dtype, int in_stride, const void* q_lat, const float* w_c,
+                                    float eps, const float* inv_freq, int rot_dims, int interleaved,
+                                    const int* positions, const int* slots, int tokens, int nh, int d, int r, int c_dim,
+                                    int page_size, long long cache_slots, void* q_out, void* k_cache, void* v_cache,
+                                    int* err, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (nh <= 0 || d <= 0 || r < 0 || c_dim <= 0 || c_dim + r > MAX_VEC || rot_dims < 0 || rot_dims > r ||
+      (rot_dims & 1) || page_size <= 0)
+    return B200_BAD_SIZE;
+  const long long work = static_cast<long long>(tokens) * (nh + 1);
+  const unsigned blocks = static_cast<unsigned>((work + WARPS - 1) / WARPS);
+  if (dtype == B200_F32)
+    latent_prepare_kernel<float><<<blocks, WARPS * 32, 0, stream>>>(
+        static_cast<const float*>(x), in_stride, static_cast<const float*>(q_lat), w_c, eps, inv_freq, rot_dims,
+        interleaved, positions, slots, tokens, nh, d, r, c_dim, page_size, cache_slots, static_cast<float*>(q_out),
+        static_cast<float*>(k_cache), static_cast<float*>(v_cache), err);
+  else if (dtype == B200_BF16)
+    latent_prepare_kernel<__nv_bfloat16><<<blocks, WARPS * 32, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(x), in_stride, static_cast<const __nv_bfloat16*>(q_lat), w_c, eps, inv_freq,
+        rot_dims, interleaved, positions, slots, tokens, nh, d, r, c_dim, page_size, cache_slots,
+        static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache),
+        err);
+  else
+    return B200_BAD_DTYPE;
+  return b200_check_launch();
+}

@@ -4,6 +4,10 @@
 //                        vector, powers taken element by element; (a, b, c, e) are four floats on the device
 //   head_unit_norm_gate  out[t][h][:] = o[t][h][:] / sqrt(mean(o[t][h][:]^2) + eps) * silu(g[t][h][:])
 //   sigmoid_gate_mul     out[t][c] = a[t][c] * sigmoid(g[t][c])
+//   activate_columns     x[t][c] <- act(x[t][c]) for the first `columns` columns of rows `stride` wide (in place), or
+//                        out[t][c] = act(x[t][c]); act: 1 silu, 2 gelu with erf, 3 gelu with tanh
+//   row_norm_gate        out[t][:] = o[t][:] / sqrt(mean(o[t][:]^2) + eps) * w[:] * sigmoid(g[t][:])   (o in float)
+//   tanh_cap             z <- cap * tanh(z / cap) in place on floats
 //
 // `g` is a column range of a wider matrix (row stride g_stride), so a gate that was projected together with
 // other things is read where it lies.
@@ -190,5 +194,83 @@ B200_EXPORT int b200_sigmoid_gate_mul(void* out, const void* a, const void* g, i
         g_stride, width);
   else
     return B200_BAD_DTYPE;
+  return b200_check_launch();
+}
+
+// ------------------------------------------------------------------ activations, a joint norm with a gate, a cap
+enum : int { ACT_SILU = 1, ACT_GELU_ERF = 2, ACT_GELU_TANH = 3 };
+
+__device__ __forceinline__ float activate(float z, int act) {
+  if (act == ACT_SILU) return z / (1.0f + expf(-z));
+  if (act == ACT_GELU_ERF) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
+  if (act == ACT_GELU_TANH) return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+  return z;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+activate_columns_kernel(T* out, int out_stride, const T* x, int stride, int columns, int act) {   // out may be x
+  const size_t t = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c < columns) out[t * out_stride + c] = from_f32<T>(activate(to_f32<T>(x[t * stride + c]), act));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+row_norm_gate_kernel(T* __restrict__ out, const float* __restrict__ o, const float* __restrict__ w,
+                     const T* __restrict__ g, int g_stride, int width, float eps) {
+  __shared__ float scratch[33];
+  const size_t t = blockIdx.x;
+  const float* src = o + t * width;
+  float ss = 0.0f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) ss = fmaf(src[c], src[c], ss);
+  ss = block_sum(ss, scratch);
+  const float r = 1.0f / sqrtf(ss / static_cast<float>(width) + eps);
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float x = to_f32<T>(g[t * g_stride + c]);
+    out[t * width + c] = from_f32<T>(src[c] * r * w[c] / (1.0f + expf(-x)));
+  }
+}
+
+__global__ void __launch_bounds__(256) tanh_cap_kernel(float* z, long long n, float cap) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) z[i] = cap * tanhf(z[i] / cap);
+}
+
+B200_EXPORT int b200_activate_columns(void* out, int out_stride, const void* x, int stride, int tokens, int columns,
+                                      int act, int dtype, cudaStream_t stream) {
+  if (tokens <= 0 || columns <= 0) return 0;
+  if (act < ACT_SILU || act > ACT_GELU_TANH || stride < columns || out_stride < columns) return B200_BAD_SIZE;
+  const dim3 grid(tokens, (columns + 255) / 256);
+  if (dtype == B200_F32)
+    activate_columns_kernel<float><<<grid, 256, 0, stream>>>(static_cast<float*>(out), out_stride,
+                                                             static_cast<const float*>(x), stride, columns, act);
+  else if (dtype == B200_BF16)
+    activate_columns_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
+        static_cast<__nv_bfloat16*>(out), out_stride, static_cast<const __nv_bfloat16*>(x), stride, columns, act);
+  else
+    return B200_BAD_DTYPE;
+  return b200_check_launch();
+}
+
+B200_EXPORT int b200_row_norm_gate(void* out, const float* o, const float* w, const void* g, int g_stride, int tokens,
+                                   int width, float eps, int dtype, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (width <= 0) return B200_BAD_SIZE;
+  if (dtype == B200_F32)
+    row_norm_gate_kernel<float><<<tokens, 256, 0, stream>>>(static_cast<float*>(out), o, w,
+                                                            static_cast<const float*>(g), g_stride, width, eps);
+  else if (dtype == B200_BF16)
+    row_norm_gate_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>(
+        static_cast<__nv_bfloat16*>(out), o, w, static_cast<const __nv_bfloat16*>(g), g_stride, width, eps);
+  else
+    return B200_BAD_DTYPE;
+  return b200_check_launch();
+}
+
+B200_EXPORT int b200_tanh_cap(float* z, long long n, float cap, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (!(cap > 0.0f)) return B200_BAD_SIZE;
+  tanh_cap_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(z, n, cap);
   return b200_check_launch();
 }

@@ -6,6 +6,10 @@
 // Every output element is accumulated over k = 0, 1, ..., K-1 in that order,
 // whatever M and N are and wherever the element sits in a tile, so a token's
 // result is bit-identical however the batch around it is cut.
+//
+// The batched form multiplies `batch` independent pairs whose rows may lie apart (leading dimensions lda, ldw, ldc
+// and a distance between consecutive matrices of each operand): per-head products of a mixer, where head h's rows are
+// column ranges of wider matrices.
 #include "common.cuh"
 
 constexpr int BM = 64, BN = 64, BK = 16;
@@ -13,7 +17,10 @@ constexpr int BM = 64, BN = 64, BK = 16;
 template <bool VEC>
 __global__ void __launch_bounds__(256)
 sgemm_nt_kernel(const float* __restrict__ A, const float* __restrict__ W, float* __restrict__ C,
-                int M, int N, int K) {
+                int M, int N, int K, int lda, int ldw, int ldc, long long step_a, long long step_w, long long step_c) {
+  A += blockIdx.z * step_a;
+  W += blockIdx.z * step_w;
+  C += blockIdx.z * step_c;
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -30,13 +37,13 @@ sgemm_nt_kernel(const float* __restrict__ A, const float* __restrict__ W, float*
     float a[4] = {0.f, 0.f, 0.f, 0.f}, w[4] = {0.f, 0.f, 0.f, 0.f};
     const int am = m0 + lrow, wn = n0 + lrow, kk = k0 + lk;
     if (VEC) {
-      if (am < M && kk < K) { const float4 v = *reinterpret_cast<const float4*>(A + static_cast<size_t>(am) * K + kk); a[0] = v.x; a[1] = v.y; a[2] = v.z; a[3] = v.w; }
-      if (wn < N && kk < K) { const float4 v = *reinterpret_cast<const float4*>(W + static_cast<size_t>(wn) * K + kk); w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w; }
+      if (am < M && kk < K) { const float4 v = *reinterpret_cast<const float4*>(A + static_cast<size_t>(am) * lda + kk); a[0] = v.x; a[1] = v.y; a[2] = v.z; a[3] = v.w; }
+      if (wn < N && kk < K) { const float4 v = *reinterpret_cast<const float4*>(W + static_cast<size_t>(wn) * ldw + kk); w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w; }
     } else {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        if (am < M && kk + i < K) a[i] = A[static_cast<size_t>(am) * K + kk + i];
-        if (wn < N && kk + i < K) w[i] = W[static_cast<size_t>(wn) * K + kk + i];
+        if (am < M && kk + i < K) a[i] = A[static_cast<size_t>(am) * lda + kk + i];
+        if (wn < N && kk + i < K) w[i] = W[static_cast<size_t>(wn) * ldw + kk + i];
       }
     }
     __syncthreads();
@@ -61,7 +68,7 @@ sgemm_nt_kernel(const float* __restrict__ A, const float* __restrict__ W, float*
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tx * 4 + j;
-      if (n < N) C[static_cast<size_t>(m) * N + n] = acc[i][j];
+      if (n < N) C[static_cast<size_t>(m) * ldc + n] = acc[i][j];
     }
   }
 }
@@ -71,7 +78,22 @@ B200_EXPORT int b200_gemm_f32(const float* a, const float* w, float* c, int m, i
   if (k <= 0) return B200_BAD_SIZE;
   dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM);
   const bool vec = (k % 4 == 0) && (reinterpret_cast<uintptr_t>(a) % 16 == 0) && (reinterpret_cast<uintptr_t>(w) % 16 == 0);
-  if (vec) sgemm_nt_kernel<true><<<grid, 256, 0, stream>>>(a, w, c, m, n, k);
-  else sgemm_nt_kernel<false><<<grid, 256, 0, stream>>>(a, w, c, m, n, k);
+  if (vec) sgemm_nt_kernel<true><<<grid, 256, 0, stream>>>(a, w, c, m, n, k, k, k, n, 0, 0, 0);
+  else sgemm_nt_kernel<false><<<grid, 256, 0, stream>>>(a, w, c, m, n, k, k, k, n, 0, 0, 0);
+  return b200_check_launch();
+}
+
+// c[b] (m x n, rows ldc apart) = a[b] (m x k, rows lda apart) . w[b] (n x k, rows ldw apart)^T for b < batch; matrix b
+// of an operand starts step_* floats behind matrix b - 1.
+B200_EXPORT int b200_gemm_f32_batched(const float* a, const float* w, float* c, int m, int n, int k, int batch, int lda,
+                                      int ldw, int ldc, long long step_a, long long step_w, long long step_c,
+                                      cudaStream_t stream) {
+  if (m <= 0 || n <= 0 || batch <= 0) return 0;
+  if (k <= 0 || lda < k || ldw < k || ldc < n || batch > 65535) return B200_BAD_SIZE;
+  dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM, batch);
+  const bool vec = (k % 4 == 0) && (lda % 4 == 0) && (ldw % 4 == 0) && (step_a % 4 == 0) && (step_w % 4 == 0) &&
+                   (reinterpret_cast<uintptr_t>(a) % 16 == 0) && (reinterpret_cast<uintptr_t>(w) % 16 == 0);
+  if (vec) sgemm_nt_kernel<true><<<grid, 256, 0, stream>>>(a, w, c, m, n, k, lda, ldw, ldc, step_a, step_w, step_c);
+  else sgemm_nt_kernel<false><<<grid, 256, 0, stream>>>(a, w, c, m, n, k, lda, ldw, ldc, step_a, step_w, step_c);
   return b200_check_launch();
 }

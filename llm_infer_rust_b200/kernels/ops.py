@@ -291,7 +291,8 @@ def tcgen05_attention_launches() -> tuple:
 def prefill_attention(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefix_len, rows, n_rows,
                       max_q_len, num_heads, num_kv_heads, head_dim, page_size, window, scale,
                       tiles_per_cta: int = 0, v_head_dim: Optional[int] = None, softcap: float = 0.0,
-                      precise_weights: bool = False) -> None:
+                      precise_weights: bool = False, chunk: Optional[int] = None,
+                      sinks: Optional[torch.Tensor] = None) -> None:
     """Causal attention of prompt portions over the paged cache (rows: which batch rows).
 
     ``v_head_dim``: the width of a value (and of an output) vector where it differs from a key's;
@@ -300,17 +301,23 @@ def prefill_attention(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefi
     another width than keys take the all-sizes kernel, whose weights are floats; a soft-cap or precise weights take
     the mma.sync kernel, not the tcgen05 one (whose weights are single bfloat16 numbers in tensor memory).
 
+    ``chunk`` C: a query at position p sees only keys from p - p % C on (its own block of C positions, counted from
+    the sequence's start); ``sinks`` (float32, one per query head): exp(sink) joins the softmax's denominator.  Both
+    take the all-sizes kernel.
+
     ``tiles_per_cta`` (head size 128 on the tcgen05 kernel only): 1 or 2 tiles of 128 query vectors per
     CTA, 0 lets the kernel's launcher choose by the size of the grid."""
-    _cuda(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefix_len, rows)
-    _contig(q, k_cache, v_cache, out, block_table)
+    _cuda(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefix_len, rows, sinks)
+    _contig(q, k_cache, v_cache, out, block_table, sinks)
     if n_rows == 0:
         return
     if k_cache.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelError("q, cache and output must share a dtype")
     dv = int(v_head_dim or head_dim)
     cap = float(softcap or 0.0)
-    if dv == head_dim and decode_uses_tensor_cores(q.dtype, num_heads, num_kv_heads, head_dim, page_size):
+    _check_sinks(sinks, num_heads)
+    plain_mask = not chunk and sinks is None
+    if plain_mask and dv == head_dim and decode_uses_tensor_cores(q.dtype, num_heads, num_kv_heads, head_dim, page_size):
         if k_cache.shape[1] != num_kv_heads or k_cache.shape[2] != page_size:
             raise KernelError("the cache must be [pages + 1, kv_heads, page_size, head_dim]")
         box_rows = min(page_size, 32)
@@ -334,8 +341,14 @@ def prefill_attention(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefi
     rc = _attention(max(head_dim, dv)).b200_prefill_attention(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(block_table), block_table.shape[-1], _p(cu_q),
         _p(kv_len), _p(prefix_len), _p(rows), n_rows, max_q_len, num_heads, num_kv_heads, page_size,
-        int(window or 0), ctypes.c_float(scale), _code(q), head_dim, dv, ctypes.c_float(cap), _stream())
+        int(window or 0), ctypes.c_float(scale), _code(q), head_dim, dv, ctypes.c_float(cap), int(chunk or 0),
+        _p(sinks), _stream())
     _ok(rc, "prefill_attention")
+
+
+def _check_sinks(sinks: Optional[torch.Tensor], num_heads: int) -> None:
+    if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != num_heads):
+        raise KernelError("sinks must be float32, one per query head")
 
 
 MMA_MAX_GROUP = 16
@@ -392,17 +405,19 @@ def decode_scratch_floats(n_rows: int, num_heads: int, head_dim: int, splits: in
 
 def decode_attention(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_len, rows, n_rows,
                      num_heads, num_kv_heads, head_dim, page_size, window, scale, splits,
-                     v_head_dim: Optional[int] = None, softcap: float = 0.0, precise_weights: bool = False) -> None:
+                     v_head_dim: Optional[int] = None, softcap: float = 0.0, precise_weights: bool = False,
+                     chunk: Optional[int] = None, sinks: Optional[torch.Tensor] = None) -> None:
     """Attention of single decoded tokens, the keys split over ``splits`` blocks per row (``v_head_dim``,
-    ``softcap``, ``precise_weights``: see ``prefill_attention``)."""
-    _cuda(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_len, rows)
-    _contig(q, k_cache, v_cache, out, block_table, scratch)
+    ``softcap``, ``precise_weights``, ``chunk``, ``sinks``: see ``prefill_attention``)."""
+    _cuda(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_len, rows, sinks)
+    _contig(q, k_cache, v_cache, out, block_table, scratch, sinks)
+    _check_sinks(sinks, num_heads)
     if n_rows == 0:
         return
     if k_cache.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelError("q, cache and output must share a dtype")
     dv = int(v_head_dim or head_dim)
-    plain = dv == head_dim
+    plain = dv == head_dim and not chunk and sinks is None
     need = decode_scratch_floats(n_rows, num_heads, max(head_dim, dv), splits)
     if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
         raise KernelError(f"decode attention needs {need} floats of scratch")
@@ -421,7 +436,8 @@ def decode_attention(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_le
     rc = _attention(max(head_dim, dv)).b200_decode_attention(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(scratch), _p(block_table), block_table.shape[-1],
         _p(cu_q), _p(kv_len), _p(rows), n_rows, num_heads, num_kv_heads, page_size, int(window or 0),
-        ctypes.c_float(scale), splits, _code(q), head_dim, dv, ctypes.c_float(softcap or 0.0), _stream())
+        ctypes.c_float(scale), splits, _code(q), head_dim, dv, ctypes.c_float(softcap or 0.0), int(chunk or 0),
+        _p(sinks), _stream())
     _ok(rc, "decode_attention", 2 if splits > 1 else 1)
 
 
@@ -1178,6 +1194,33 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = Non
     return out
 
 
+def head_products(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One small product per head: out[h] = x[h] . weight[h]^T with x [heads, rows, k] (any strides with a unit inner
+    one, so a head may be a column range of a wider matrix), weight [heads, n, k] contiguous, out [heads, rows, n]
+    (given: any strides with a unit inner one).  float32: this package's 32-bit kernel; bfloat16: the library's
+    batched product with float accumulation."""
+    _cuda(x, weight, out)
+    heads, rows, k = x.shape
+    n = weight.shape[1]
+    if weight.shape[0] != heads or weight.shape[2] != k or not weight.is_contiguous() or x.stride(2) != 1 \
+            or x.dtype != weight.dtype:
+        raise KernelError("head_products takes x [heads, rows, k] and contiguous weights [heads, n, k] of one dtype")
+    if out is None:
+        out = torch.empty((heads, rows, n), dtype=x.dtype, device=x.device)
+    elif tuple(out.shape) != (heads, rows, n) or out.stride(2) != 1 or out.dtype != x.dtype:
+        raise KernelError("head_products: the output must be [heads, rows, n] with a unit inner stride")
+    if x.dtype == torch.float32:
+        rc = load_cuda_library("gemm_f32.cu").b200_gemm_f32_batched(
+            _p(x), _p(weight), _p(out), rows, n, k, heads, x.stride(1), k, out.stride(1),
+            ctypes.c_longlong(x.stride(0)), ctypes.c_longlong(n * k), ctypes.c_longlong(out.stride(0)), _stream())
+        _ok(rc, "gemm_f32_batched")
+        return out
+    if x.dtype != torch.bfloat16:
+        raise KernelError("head_products takes float32 or bfloat16")
+    torch.bmm(x, weight.transpose(1, 2), out=out)
+    return out
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
            lazy: bool = False) -> torch.Tensor:
     """x[M, K] . weight[N, K]^T, no bias.  ``lazy``: see ``few_row_linear``.
@@ -1476,3 +1519,176 @@ def sigmoid_gate_mul(a: torch.Tensor, packed: torch.Tensor, gate_column: int) ->
                                         a.shape[1], _code(a), _stream())
     _ok(rc, "sigmoid_gate_mul")
     return a
+
+
+# --------------------------------------------------------------------------- activations, joint norm with a gate, caps
+ACTIVATIONS = {"silu": 1, "gelu_erf": 2, "gelu_tanh": 3}
+
+
+def activate(x: torch.Tensor, act: str, columns: Optional[int] = None, in_place: bool = False) -> torch.Tensor:
+    """act(x) element by element on the first ``columns`` columns of x [tokens, width] (all by default): silu,
+    gelu_erf (the exact one) or gelu_tanh; computed in float, rounded once.  ``in_place``: x itself is changed."""
+    _cuda(x)
+    _contig(x)
+    if act not in ACTIVATIONS or x.dim() != 2:
+        raise KernelError(f"activation {act!r} is refused: {sorted(ACTIVATIONS)} on [tokens, width]")
+    c = int(columns if columns is not None else x.shape[1])
+    out = x if in_place else torch.empty((x.shape[0], c), dtype=x.dtype, device=x.device)
+    rc = _gated().b200_activate_columns(_p(out), out.shape[1], _p(x), x.shape[1], x.shape[0], c, ACTIVATIONS[act],
+                                        _code(x), _stream())
+    _ok(rc, "activate_columns")
+    return out
+
+
+def row_norm_gate(o: torch.Tensor, weight: torch.Tensor, packed: torch.Tensor, gate_column: int, eps: float) -> torch.Tensor:
+    """o (float32 [tokens, width]) divided by each row's root mean square, times ``weight``, times sigmoid of the
+    gate that lies in ``packed`` from column ``gate_column`` on; the result has ``packed``'s dtype."""
+    _cuda(o, weight, packed)
+    _contig(o, weight, packed)
+    _f32(o, weight)
+    if packed.shape[1] < gate_column + o.shape[1] or weight.numel() != o.shape[1]:
+        raise KernelError("row_norm_gate: the gate's columns or the weight do not fit")
+    out = torch.empty(o.shape, dtype=packed.dtype, device=o.device)
+    gate = packed.view(-1)[gate_column:]
+    rc = _gated().b200_row_norm_gate(_p(out), _p(o), _p(weight), ctypes.c_void_p(gate.data_ptr()), packed.shape[1],
+                                     o.shape[0], o.shape[1], ctypes.c_float(eps), _code(packed), _stream())
+    _ok(rc, "row_norm_gate")
+    return out
+
+
+def tanh_cap(z: torch.Tensor, cap: float) -> torch.Tensor:
+    """z <- cap * tanh(z / cap), in place on float32."""
+    _cuda(z)
+    _contig(z)
+    _f32(z)
+    rc = _gated().b200_tanh_cap(_p(z), ctypes.c_longlong(z.numel()), ctypes.c_float(cap), _stream())
+    _ok(rc, "tanh_cap")
+    return z
+
+
+# --------------------------------------------------------------------------- a residual of several streams
+MAX_STREAMS = 8
+
+
+def stream_step(streams: torch.Tensor, norm_weight: torch.Tensor, offset: float, eps: float, out_dtype: torch.dtype,
+                start: Optional[torch.Tensor] = None, y: Optional[torch.Tensor] = None,
+                before: Optional[torch.Tensor] = None, read_in: Optional[torch.Tensor] = None,
+                rows: Optional[torch.Tensor] = None, store: bool = True) -> torch.Tensor:
+    """One write-back and read of a residual held as S float32 streams [tokens, S, width].
+
+    With ``start`` ([tokens, width] float32) every stream becomes a copy of it; else, with ``before`` (the packed
+    coefficients in[S], out[S], mix[S, S] of the sublayer whose output ``y`` is), X_t <- sum_s mix[s, t] X_s +
+    out[t] y for all t at once.  Then u = sum_s read_in[s] X_s (ones without ``read_in``) and the result is
+    u / sqrt(mean(u^2) + eps) * (norm_weight + offset), rounded once to ``out_dtype``; for ``rows`` only if given.
+    ``store`` False leaves the streams unwritten (the model's last read)."""
+    _cuda(streams, norm_weight, start, y, before, read_in, rows)
+    _contig(streams, norm_weight, start, y, before, read_in, rows)
+    _f32(streams, norm_weight, start, before, read_in)
+    _i32(rows)
+    tokens, s, width = streams.shape
+    if not 1 <= s <= MAX_STREAMS or norm_weight.numel() != width:
+        raise KernelError(f"stream_step takes 1 to {MAX_STREAMS} streams and a weight per column")
+    if before is not None and (y is None or before.numel() != s * (s + 2) or tuple(y.shape) != (tokens, width)):
+        raise KernelError("stream_step: the write-back needs y [tokens, width] and in, out, mix of its sublayer")
+    if start is not None and tuple(start.shape) != (tokens, width):
+        raise KernelError("stream_step: the start must be [tokens, width]")
+    if read_in is not None and read_in.numel() != s:
+        raise KernelError("stream_step: one read coefficient per stream")
+    n = tokens if rows is None else rows.numel()
+    out = torch.empty((n, width), dtype=out_dtype, device=streams.device)
+    rc = load_cuda_library("residual_streams.cu").b200_stream_step(
+        _p(streams), s, _p(start), _p(y), _code(y) if y is not None else F32, _p(before), _p(read_in), _p(norm_weight),
+        ctypes.c_float(offset), ctypes.c_float(eps), _p(rows), _p(out), _code(out), n, width, int(bool(store)), _stream())
+    _ok(rc, "stream_step")
+    return out
+
+
+# --------------------------------------------------------------------------- between a packed projection and attention
+def heads_prepare(x: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                  positions: torch.Tensor, slots: Optional[torch.Tensor], num_heads: int, num_kv_heads: int,
+                  head_dim: int, v_head_dim: int, bias: Optional[torch.Tensor] = None,
+                  q_weight: Optional[torch.Tensor] = None, k_weight: Optional[torch.Tensor] = None, eps: float = 0.0,
+                  inv_freq: Optional[torch.Tensor] = None, rot_dims: int = 0, interleaved: bool = True) -> None:
+    """q, k, v are the first columns of ``x``: optional bias (float32, one per column), optional per-head RMS norm
+    of q and k (float32 weights over a head), optional rotation of the first ``rot_dims`` coordinates of every q
+    and k head by position * inv_freq (pairs (2i, 2i+1) if ``interleaved`` else (i, i + rot_dims/2)); q to ``q_out``,
+    k and v into the paged cache at ``slots`` (None: nothing is stored)."""
+    _cuda(x, q_out, k_cache, v_cache, positions, slots, bias, q_weight, k_weight, inv_freq)
+    _contig(x, q_out, k_cache, v_cache, positions, slots, bias, q_weight, k_weight, inv_freq)
+    _f32(bias, q_weight, k_weight, inv_freq)
+    c = (num_heads + num_kv_heads) * head_dim + num_kv_heads * v_head_dim
+    if x.shape[1] < c or q_out.dtype != x.dtype or k_cache.dtype != x.dtype or v_cache.dtype != x.dtype:
+        raise KernelError("heads_prepare: the projection is too narrow, or q, cache and projection differ in dtype")
+    if tuple(k_cache.shape[1:]) != (num_kv_heads, k_cache.shape[2], head_dim) or \
+            tuple(v_cache.shape[1:]) != (num_kv_heads, k_cache.shape[2], v_head_dim):
+        raise KernelError("the cache must be [pages + 1, kv_heads, page_size, width]")
+    if (bias is not None and bias.numel() != c) or (q_weight is None) != (k_weight is None) or \
+            (q_weight is not None and (q_weight.numel() != head_dim or k_weight.numel() != head_dim)):
+        raise KernelError("heads_prepare: bias or norm weights of the wrong size")
+    if inv_freq is not None and inv_freq.numel() * 2 != rot_dims:
+        raise KernelError("one frequency for every rotated pair is needed")
+    page_size = k_cache.shape[2]
+    rc = load_cuda_library("attention_prepare.cu").b200_heads_prepare(
+        _p(x), _code(x), x.shape[1], _p(bias), _p(q_weight), _p(k_weight), ctypes.c_float(eps), _p(inv_freq),
+        int(rot_dims if inv_freq is not None else 0), int(bool(interleaved)), _p(positions), _p(slots), x.shape[0],
+        num_heads, num_kv_heads, head_dim, v_head_dim, page_size, ctypes.c_longlong(k_cache.shape[0] * page_size),
+        _p(q_out), _p(k_cache), _p(v_cache), _p(error_word(x.device)), _stream())
+    _ok(rc, "heads_prepare")
+
+
+def latent_prepare(x: torch.Tensor, q_lat: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor,
+                   v_cache: torch.Tensor, latent_weight: torch.Tensor, eps: float, positions: torch.Tensor,
+                   slots: Optional[torch.Tensor], num_heads: int, head_dim: int, rot_dim: int, latent_dim: int,
+                   inv_freq: Optional[torch.Tensor] = None, rot_dims: int = 0, interleaved: bool = True) -> None:
+    """``x`` holds per head [head_dim plain | rot_dim rotated] query coordinates, then [latent_dim | rot_dim] of the
+    down projection.  The latent is RMS-normed (``latent_weight``) and stored with the rotated key part behind it as
+    the token's one key [latent_dim + rot_dim] and alone as its value; the query that meets such keys is
+    [q_lat[h, t] | rotated part] and goes to ``q_out`` [tokens, heads * (latent_dim + rot_dim)]."""
+    _cuda(x, q_lat, q_out, k_cache, v_cache, latent_weight, positions, slots, inv_freq)
+    _contig(x, q_lat, q_out, k_cache, v_cache, latent_weight, positions, slots, inv_freq)
+    _f32(latent_weight, inv_freq)
+    tokens = x.shape[0]
+    if x.shape[1] < num_heads * (head_dim + rot_dim) + latent_dim + rot_dim or \
+            tuple(q_lat.shape) != (num_heads, tokens, latent_dim) or latent_weight.numel() != latent_dim or \
+            q_lat.dtype != x.dtype or q_out.dtype != x.dtype or k_cache.dtype != x.dtype or v_cache.dtype != x.dtype:
+        raise KernelError("latent_prepare: sizes or dtypes do not fit")
+    if tuple(k_cache.shape[1:]) != (1, k_cache.shape[2], latent_dim + rot_dim) or \
+            tuple(v_cache.shape[1:]) != (1, k_cache.shape[2], latent_dim):
+        raise KernelError("the latent cache must be [pages + 1, 1, page_size, latent_dim + rot_dim] and [.., latent_dim]")
+    if inv_freq is not None and inv_freq.numel() * 2 != rot_dims:
+        raise KernelError("one frequency for every rotated pair is needed")
+    page_size = k_cache.shape[2]
+    rc = load_cuda_library("attention_prepare.cu").b200_latent_prepare(
+        _p(x), _code(x), x.shape[1], _p(q_lat), _p(latent_weight), ctypes.c_float(eps), _p(inv_freq),
+        int(rot_dims if inv_freq is not None else 0), int(bool(interleaved)), _p(positions), _p(slots), tokens,
+        num_heads, head_dim, rot_dim, latent_dim, page_size, ctypes.c_longlong(k_cache.shape[0] * page_size),
+        _p(q_out), _p(k_cache), _p(v_cache), _p(error_word(x.device)), _stream())
+    _ok(rc, "latent_prepare")
+
+
+# --------------------------------------------------------------------------- experts chosen by a table
+def table_experts(x: torch.Tensor, token_ids: torch.Tensor, table: torch.Tensor, gate_up: torch.Tensor,
+                  down: torch.Tensor) -> torch.Tensor:
+    """out[t] = (1 / top) sum_k down[e] (silu(gate[e] x_t) * (up[e] x_t)), e = table[token_ids[t], k]; float32
+    [tokens, width].  gate_up [experts, 2 ff, width] (gate rows, then up rows), down [experts, width, ff]."""
+    _cuda(x, token_ids, table, gate_up, down)
+    _contig(x, token_ids, table, gate_up, down)
+    _i32(token_ids, table)
+    tokens, width = x.shape
+    experts, ff2, _ = gate_up.shape
+    ff = ff2 // 2
+    vocab, top = table.shape
+    if gate_up.dtype != x.dtype or down.dtype != x.dtype or tuple(down.shape) != (experts, width, ff) \
+            or gate_up.shape[2] != width or token_ids.numel() != tokens:
+        raise KernelError("table_experts: sizes or dtypes do not fit")
+    lib = load_cuda_library("experts.cu")
+    lib.b200_expert_route_ints.restype = ctypes.c_longlong
+    pairs = tokens * top
+    route = torch.empty(int(lib.b200_expert_route_ints(tokens, top, experts)), dtype=torch.int32, device=x.device)
+    h = torch.empty((pairs, ff), dtype=x.dtype, device=x.device)
+    y = torch.empty((pairs, width), dtype=torch.float32, device=x.device)
+    out = torch.empty((tokens, width), dtype=torch.float32, device=x.device)
+    rc = lib.b200_table_experts(_p(x), _code(x), _p(token_ids), _p(table), vocab, top, experts, _p(gate_up), _p(down),
+                                tokens, width, ff, _p(h), _p(y), _p(route), _p(out), _p(error_word(x.device)), _stream())
+    _ok(rc, "table_experts", 4)
+    return out

@@ -241,5 +241,207 @@ class GatedConvAttention(Part):
         return ops.linear(out, p["o_proj"])
 
 
+def _masked_attention(part, q, out, ctx, cache, num_heads, num_kv_heads, head_dim, v_head_dim, sinks):
+    """Attention of a step's rows over the paged cache for a mixer with ``window``, ``chunk`` and ``scale``: prompt
+    portions and single decoded tokens, softmax weights in float."""
+    g = cache.group
+    page = ctx.page_sizes[g]
+    if ctx.num_prefill:
+        ops.prefill_attention(q, cache.k, cache.v, out, ctx.block_tables[g], ctx.cu_q, ctx.kv_len,
+                              ctx.prefix_len, ctx.prefill_rows, ctx.num_prefill, ctx.max_q_len,
+                              num_heads, num_kv_heads, head_dim, page, part.window, part.scale,
+                              v_head_dim=v_head_dim, precise_weights=True, chunk=part.chunk, sinks=sinks)
+    if ctx.num_decode:
+        bound = ctx.kv_len_bound
+        for limit in (part.window, part.chunk):
+            if limit:
+                bound = min(bound, limit)
+        plain = v_head_dim == head_dim and not part.chunk and sinks is None
+        per_split = ops.decode_ctas_per_split(q.dtype, ctx.num_decode, num_heads, num_kv_heads, head_dim, page, plain)
+        splits = decode_splits(per_split, bound, ctx.sm_count)
+        need = ops.decode_scratch_floats(ctx.num_decode, num_heads, max(head_dim, v_head_dim), splits)
+        scratch = ctx.scratch(need) if need else None
+        ops.decode_attention(q, cache.k, cache.v, out, scratch, ctx.block_tables[g], ctx.cu_q,
+                             ctx.kv_len, ctx.decode_rows, ctx.num_decode, num_heads, num_kv_heads, head_dim,
+                             page, part.window, part.scale, splits, v_head_dim=v_head_dim, precise_weights=True,
+                             chunk=part.chunk, sinks=sinks)
+
+
+class GroupedAttention(Part):
+    """Grouped-query softmax attention over the paged cache with keys ``head_dim`` wide and values ``v_head_dim``
+    wide, from one packed projection (q rows, k rows, v rows, then gate rows if gated).  Each of these is a
+    parameter of the part and may be absent:
+      * ``bias``: q, k and v have biases (one packed vector, added in float before anything else);
+      * ``qk_norm_eps``: q and k are RMS-normed per head with one weight vector each (``q_norm``, ``k_norm``);
+      * ``position_encoding`` / ``rot_dims``: the first rot_dims coordinates of every q and k head are rotated
+        (the encoding says whether pairs are interleaved or half-split);
+      * ``window`` W: a query at position p reads keys p - W < j <= p;  ``chunk`` C: only keys from p - p % C on
+        (its own block of C positions, blocks counted from the sequence's start); both masks may be set;
+      * ``sink``: a learned number per head whose exponential joins the softmax's denominator (no key, no value,
+        not scaled);
+      * ``gate``: the heads' outputs are multiplied by sigmoid(g) before the output projection.
+    Softmax weights stay floats."""
+    category = "mixer"
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = int(spec["hidden_size"])
+        self.nh = int(spec["num_heads"])
+        self.nkv = int(spec["num_kv_heads"])
+        self.d = int(spec["head_dim"])
+        self.dv = int(spec.get("v_head_dim") or self.d)
+        self.bias = bool(spec.get("bias", False))
+        self.qk_eps = spec.get("qk_norm_eps")
+        self.window = spec.get("window")
+        self.chunk = spec.get("chunk")
+        self.scale = float(spec.get("softmax_scale", 1.0 / math.sqrt(self.d)))
+        self.sink = bool(spec.get("sink", False))
+        self.gate = bool(spec.get("gate", False))
+        if self.nh % self.nkv:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        for width in (self.d, self.dv):
+            if width % 2 or not 2 <= width <= 512:
+                raise ValueError(f"head size {width} is refused: the attention kernels take even head sizes up to 512")
+        name = spec.get("position_encoding")
+        self.rope = env.position_encodings[name] if name else None
+        self.rot_dims = int(spec.get("rot_dims") or (self.rope.rot_dim if self.rope else 0))
+        if self.rope is not None and (self.rot_dims != self.rope.rot_dim or self.rot_dims > self.d):
+            raise ValueError("the rotation does not fit the head or the encoding")
+        self.qkv_channels = (self.nh + self.nkv) * self.d + self.nkv * self.dv
+
+    def param_decls(self):
+        rows = self.qkv_channels + (self.nh * self.dv if self.gate else 0)
+        decls = {"qkv_proj": ParamDecl((rows, self.hidden)), "o_proj": ParamDecl((self.hidden, self.nh * self.dv))}
+        if self.bias:
+            decls["qkv_bias"] = ParamDecl((self.qkv_channels,), "vector")
+        if self.qk_eps is not None:
+            decls["q_norm"] = ParamDecl((self.d,), "vector")
+            decls["k_norm"] = ParamDecl((self.d,), "vector")
+        if self.sink:
+            decls["sink"] = ParamDecl((self.nh,), "vector")
+        return decls
+
+    def bind(self, name, tensor):
+        super().bind(name, tensor)
+        if name in ("qkv_bias", "q_norm", "k_norm", "sink"):
+            self.params[name] = tensor.to(torch.float32).contiguous()
+
+    def cache_spec(self):
+        # a chunk's earlier blocks are never read again, but their pages are kept: only a window gives pages back
+        return PagedKVSpec(self.nkv, self.d, self.window, self.dv if self.dv != self.d else None)
+
+    def state_spec(self):
+        return None
+
+    def forward(self, x, ctx, cache):
+        p = self.params
+        tokens = x.shape[0]
+        rope = self.rope
+        packed = ops.linear(x, p["qkv_proj"])
+        q = torch.empty((tokens, self.nh * self.d), dtype=packed.dtype, device=packed.device)
+        slots = ctx.slots[cache.group] if cache.writes else None
+        ops.heads_prepare(packed, q, cache.k, cache.v, ctx.positions, slots, self.nh, self.nkv, self.d, self.dv,
+                          bias=p.get("qkv_bias"), q_weight=p.get("q_norm"), k_weight=p.get("k_norm"),
+                          eps=float(self.qk_eps or 0.0), inv_freq=rope.inv_freq if rope else None,
+                          rot_dims=self.rot_dims if rope else 0,
+                          interleaved=getattr(rope, "pairing", "half_split") == "interleaved")
+        out = torch.empty((tokens, self.nh * self.dv), dtype=packed.dtype, device=packed.device)
+        _masked_attention(self, q, out, ctx, cache, self.nh, self.nkv, self.d, self.dv, p.get("sink"))
+        if self.gate:
+            ops.sigmoid_gate_mul(out, packed, self.qkv_channels)
+        return ops.linear(out, p["o_proj"])
+
+
+class LatentAttention(Part):
+    """Attention whose keys and values are expanded from a narrow latent, so that only the latent is cached.
+
+    One packed projection gives, per head, [``head_dim`` plain | ``rot_dim`` rotated] query coordinates, then the
+    down projection [``kv_rank`` latent | ``rot_dim`` rotated key part that all heads share], then the gate rows if
+    gated.  The latent c is RMS-normed (``latent_norm``, eps ``eps``); head h's plain key is W_uk[h] c and its value
+    W_uv[h] c; score = (q_plain . k_plain + q_rot . k_rot) * scale.  Computed without ever forming a head's keys:
+
+        q_plain . (W_uk[h] c) = (W_uk[h]^T q_plain) . c,        sum_j p_j W_uv[h] c_j = W_uv[h] (sum_j p_j c_j)
+
+    so the cache holds ONE key per token, [c | k_rot] (kv_rank + rot_dim wide, one KV head for all query heads),
+    whose value is c; a head's query is [W_uk[h]^T q_plain | q_rot] and its output W_uv[h] times the attention's
+    result.  ``window``, ``chunk``, ``sink``, ``gate``, ``position_encoding`` / ``rot_dims``: as in
+    ``grouped_attention``."""
+    category = "mixer"
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = int(spec["hidden_size"])
+        self.nh = int(spec["num_heads"])
+        self.d = int(spec["head_dim"])
+        self.r = int(spec["rot_dim"])
+        self.dv = int(spec["v_head_dim"])
+        self.c = int(spec["kv_rank"])
+        self.eps = float(spec["eps"])
+        self.window = spec.get("window")
+        self.chunk = spec.get("chunk")
+        self.scale = float(spec.get("softmax_scale", 1.0 / math.sqrt(self.d + self.r)))
+        self.sink = bool(spec.get("sink", False))
+        self.gate = bool(spec.get("gate", False))
+        if (self.c + self.r) % 2 or self.c % 2 or self.c + self.r > 512:
+            raise ValueError("kv_rank and kv_rank + rot_dim must be even and at most 512 (the attention kernels' head sizes)")
+        name = spec.get("position_encoding")
+        self.rope = env.position_encodings[name] if name else None
+        self.rot_dims = int(spec.get("rot_dims") or (self.rope.rot_dim if self.rope else 0))
+        if self.rope is not None and (self.rot_dims != self.rope.rot_dim or self.rot_dims > self.r):
+            raise ValueError("the rotation does not fit the rotated part or the encoding")
+        self.q_channels = self.nh * (self.d + self.r)
+        self.gate_column = self.q_channels + self.c + self.r
+        self.uk_t = None
+
+    def param_decls(self):
+        rows = self.gate_column + (self.nh * self.dv if self.gate else 0)
+        decls = {"qdkv_proj": ParamDecl((rows, self.hidden)), "latent_norm": ParamDecl((self.c,), "vector"),
+                 "uk_proj": ParamDecl((self.nh * self.d, self.c)), "uv_proj": ParamDecl((self.nh * self.dv, self.c)),
+                 "o_proj": ParamDecl((self.hidden, self.nh * self.dv))}
+        if self.sink:
+            decls["sink"] = ParamDecl((self.nh,), "vector")
+        return decls
+
+    def bind(self, name, tensor):
+        super().bind(name, tensor)
+        if name in ("latent_norm", "sink"):
+            self.params[name] = tensor.to(torch.float32).contiguous()
+        elif name == "uk_proj":
+            # per head transposed, [heads, kv_rank, head_dim]: the product q_plain W_uk[h] as rows times rows
+            self.uk_t = tensor.view(self.nh, self.d, self.c).transpose(1, 2).contiguous()
+
+    def cache_spec(self):
+        return PagedKVSpec(1, self.c + self.r, self.window, self.c)
+
+    def state_spec(self):
+        return None
+
+    def forward(self, x, ctx, cache):
+        p = self.params
+        tokens = x.shape[0]
+        rope = self.rope
+        packed = ops.linear(x, p["qdkv_proj"])
+        q_plain = packed[:, :self.q_channels].view(tokens, self.nh, self.d + self.r)[:, :, :self.d].transpose(0, 1)
+        q_lat = ops.head_products(q_plain, self.uk_t)                                   # [heads, tokens, kv_rank]
+        width = self.c + self.r
+        q = torch.empty((tokens, self.nh * width), dtype=packed.dtype, device=packed.device)
+        slots = ctx.slots[cache.group] if cache.writes else None
+        ops.latent_prepare(packed, q_lat, q, cache.k, cache.v, p["latent_norm"], self.eps, ctx.positions, slots,
+                           self.nh, self.d, self.r, self.c, inv_freq=rope.inv_freq if rope else None,
+                           rot_dims=self.rot_dims if rope else 0,
+                           interleaved=getattr(rope, "pairing", "half_split") == "interleaved")
+        o_lat = torch.empty((tokens, self.nh * self.c), dtype=packed.dtype, device=packed.device)
+        _masked_attention(self, q, o_lat, ctx, cache, self.nh, 1, width, self.c, p.get("sink"))
+        out = torch.empty((tokens, self.nh * self.dv), dtype=packed.dtype, device=packed.device)
+        ops.head_products(o_lat.view(tokens, self.nh, self.c).transpose(0, 1),
+                          p["uv_proj"].view(self.nh, self.dv, self.c),
+                          out=out.view(tokens, self.nh, self.dv).transpose(0, 1))
+        if self.gate:
+            ops.sigmoid_gate_mul(out, packed, self.gate_column)
+        return ops.linear(out, p["o_proj"])
+
+
 register_part("mixer", "gqa_attention", GQAttention)
+register_part("mixer", "grouped_attention", GroupedAttention)
+register_part("mixer", "latent_attention", LatentAttention)
 register_part("mixer", "gated_conv_attention", GatedConvAttention)

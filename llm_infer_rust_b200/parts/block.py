@@ -1,7 +1,10 @@
 """Arrangements of a layer's parts."""
 from __future__ import annotations
 
+import torch
+
 from ..kernels import ops
+from .base import ParamDecl, Part
 from .registry import build_part, register_part
 
 
@@ -130,5 +133,79 @@ class PreNormInputConv:
         return y, x
 
 
+class StreamMix(Part):
+    """The coefficients with which one sublayer meets a residual of S streams: ``in`` [S] (what it reads),
+    ``out`` [S] (where its output goes) and ``mix`` [S, S] (how the old streams pass on, indexed [from, to]).
+    They are kept as one packed float32 vector (in, out, mix).  Without parameters (``fixed``: S = 1) it is
+    the ordinary residual sum: in = out = mix = 1."""
+    category = "stream_mix"
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.streams = int(spec.get("streams", 1))
+        self.fixed = bool(spec.get("fixed", False))
+        if self.fixed and self.streams != 1:
+            raise ValueError("fixed coefficients stand for one stream")
+        self.packed = torch.ones(3, dtype=torch.float32, device=env.device) if self.fixed else None
+
+    def param_decls(self):
+        if self.fixed:
+            return {}
+        s = self.streams
+        return {"in": ParamDecl((s,), "vector"), "out": ParamDecl((s,), "vector"), "mix": ParamDecl((s, s), "vector")}
+
+    def bind(self, name, tensor):
+        super().bind(name, tensor)
+        if all(n in self.params for n in ("in", "out", "mix")):
+            self.packed = torch.cat([self.params[n].to(torch.float32).reshape(-1) for n in ("in", "out", "mix")]).contiguous()
+
+
+class MultiStreamPreNorm:
+    """Pre-norm block over a residual of S float32 streams ("hyper-connections"; S = 1 with fixed coefficients is
+    the ordinary x <- x + sublayer(norm(x))).  For each sublayer q (the mixer, then the feed-forward if the layer
+    has one), with its coefficients in_q, out_q, mix_q:
+
+        u = sum_s in_q[s] X_s;    y = sublayer(norm_q(u));    X_t <- sum_s mix_q[s, t] X_s + out_q[t] y   (all t at once)
+
+    The write-back of a sublayer is owed to the next read: the norm part (``stream_rms_norm``) does the write-back
+    of the sublayer before, the read and the norm in one kernel, and the block returns (y of its last sublayer,
+    the carry with that sublayer's coefficients pending); the next block's first read, or the model's last norm,
+    settles it.  Parts by name: ``input_norm``, ``mixer``, ``mixer_mix`` and, all or none, ``post_mixer_norm``,
+    ``feed_forward``, ``ff_mix``.  A feed-forward that says ``needs_context`` is also given the step's context."""
+    category = "block"
+
+    def __init__(self, layer_spec, env):
+        self.spec = layer_spec
+        self.env = env
+        parts = layer_spec.parts
+        self.input_norm = build_part("norm", layer_spec["input_norm"], env)
+        self.mixer = build_part("mixer", layer_spec["mixer"], env)
+        self.mixer_mix = build_part("stream_mix", layer_spec["mixer_mix"], env)
+        self.feed_forward = build_part("feed_forward", parts["feed_forward"], env) if "feed_forward" in parts else None
+        self.post_mixer_norm = self.ff_mix = None
+        if self.feed_forward is not None:
+            self.post_mixer_norm = build_part("norm", layer_spec["post_mixer_norm"], env)
+            self.ff_mix = build_part("stream_mix", layer_spec["ff_mix"], env)
+
+    def children(self):
+        named = {"input_norm": self.input_norm, "mixer_mix": self.mixer_mix, "mixer": self.mixer,
+                 "post_mixer_norm": self.post_mixer_norm, "ff_mix": self.ff_mix, "feed_forward": self.feed_forward}
+        return {name: part for name, part in named.items() if part is not None}
+
+    def forward(self, h, residual, ctx, cache):
+        ops.flush_chain()
+        carry = self.input_norm.open(h) if residual is None else residual
+        y = self.mixer.forward(self.input_norm.read(h, carry, self.mixer_mix.packed), ctx, cache)
+        carry.pending = self.mixer_mix.packed
+        if self.feed_forward is not None:
+            x = self.post_mixer_norm.read(y, carry, self.ff_mix.packed)
+            y = self.feed_forward.forward(x, ctx) if getattr(self.feed_forward, "needs_context", False) \
+                else self.feed_forward.forward(x)
+            carry.pending = self.ff_mix.packed
+        return y, carry
+
+
+register_part("stream_mix", "stream_mix", StreamMix)
 register_part("block", "pre_norm_deferred_add", PreNormDeferredAdd)
+register_part("block", "multi_stream_pre_norm", MultiStreamPreNorm)
 register_part("block", "pre_norm_input_conv", PreNormInputConv)

@@ -27,7 +27,8 @@ class TokenEmbedding(Part):
 
 
 class LinearHead(Part):
-    """logits = x W^T in float32, no scale and no soft-cap (reference: src/layers/linear.rs:15-20).
+    """logits = x W^T in float32, no scale (reference: src/layers/linear.rs:15-20); with ``softcap`` c the logits
+    become c * tanh(logits / c), in float.
 
     With ``tied`` and no stored head the weight is the embedding table itself.
     """
@@ -39,6 +40,7 @@ class LinearHead(Part):
         self.vocab = int(spec["vocab_size"])
         self.hidden = int(spec["hidden_size"])
         self.tied = bool(spec.get("tied", False))
+        self.softcap = float(spec.get("softcap") or 0.0)
 
     def param_decls(self):
         return {"weight": ParamDecl((self.vocab, self.hidden))}
@@ -48,10 +50,11 @@ class LinearHead(Part):
 
     def forward(self, x):
         if isinstance(x, ops.PendingNorm):
-            if self.takes_pending(x.shape[0]):
+            if self.takes_pending(x.shape[0]) and not self.softcap > 0.0:
                 return ops.few_row_linear(x, self.params["weight"], ops.EPI_PLAIN_F32, lazy=True)
             x = x.materialize()
-        return ops.linear(x, self.params["weight"], out_dtype=torch.float32)
+        logits = ops.linear(x, self.params["weight"], out_dtype=torch.float32)
+        return ops.tanh_cap(logits, self.softcap) if self.softcap > 0.0 else logits
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)

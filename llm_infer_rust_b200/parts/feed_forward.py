@@ -69,5 +69,61 @@ class PolyNormFF(Part):
         return ops.linear(ops.poly_norm(z, self.params["act"], self.eps), self.params["down_proj"])
 
 
+class DenseActFF(Part):
+    """down(act(up(x))), no gate and no bias; ``activation``: gelu_erf (the exact gelu), gelu_tanh or silu,
+    computed in float on the rounded projection and rounded once."""
+    category = "feed_forward"
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = int(spec["hidden_size"])
+        self.inter = int(spec["intermediate_size"])
+        self.activation = str(spec.get("activation", "gelu_erf"))
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {self.activation!r} is refused: {sorted(ops.ACTIVATIONS)}")
+
+    def param_decls(self):
+        return {"up_proj": ParamDecl((self.inter, self.hidden)), "down_proj": ParamDecl((self.hidden, self.inter))}
+
+    def forward(self, x):
+        z = ops.linear(x, self.params["up_proj"])
+        return ops.linear(ops.activate(z, self.activation, in_place=True), self.params["down_proj"])
+
+
+class TableExperts(Part):
+    """A mixture of gated experts without a router: row ``token id`` of an integer ``table`` [vocab, top] names the
+    token's experts (the entries of a row differ), and each counts 1 / top:
+
+        y = (1 / top) sum_k down[e_k] (silu(gate[e_k] x) * (up[e_k] x))
+
+    ``gate_up_proj`` [experts * 2 ff, hidden] holds expert after expert, each its gate rows and then its up rows;
+    ``down_proj`` [experts * hidden, ff].  No biases.  The output is float32 (it is summed in float)."""
+    category = "feed_forward"
+    needs_context = True          # the choice depends on the step's token ids
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = int(spec["hidden_size"])
+        self.inter = int(spec["intermediate_size"])
+        self.experts = int(spec["experts"])
+        self.top = int(spec["top"])
+        self.vocab = int(spec["vocab_size"])
+        if not 1 <= self.top <= self.experts:
+            raise ValueError("a token takes between one and all experts")
+
+    def param_decls(self):
+        return {"gate_up_proj": ParamDecl((self.experts * 2 * self.inter, self.hidden)),
+                "down_proj": ParamDecl((self.experts * self.hidden, self.inter)),
+                "table": ParamDecl((self.vocab, self.top), "table")}
+
+    def forward(self, x, ctx):
+        p = self.params
+        return ops.table_experts(x, ctx.token_ids, p["table"],
+                                 p["gate_up_proj"].view(self.experts, 2 * self.inter, self.hidden),
+                                 p["down_proj"].view(self.experts, self.hidden, self.inter))
+
+
 register_part("feed_forward", "swiglu", SwiGLU)
+register_part("feed_forward", "dense_act", DenseActFF)
+register_part("feed_forward", "table_experts", TableExperts)
 register_part("feed_forward", "poly_norm", PolyNormFF)

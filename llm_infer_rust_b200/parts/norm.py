@@ -76,5 +76,67 @@ class ScalarRMSNorm(Part):
         return ops.scaled_rows(residual, self.scale(residual, x), rows, self.env.dtype)
 
 
+class StreamCarry:
+    """A residual held as S float32 streams [tokens, S, width], with the write-back that is still owed to it:
+    ``pending`` holds the packed coefficients (in, out, mix) of the sublayer whose output comes with the next read.
+    ``start``: the streams do not exist yet and begin as copies of this [tokens, width] float32 tensor."""
+
+    def __init__(self, streams, start=None):
+        self.streams = streams
+        self.start = start
+        self.pending = None
+
+
+class StreamRMSNorm(Part):
+    """RMS norm that reads a residual of S float32 streams (``streams``; 1: the ordinary residual sum).
+
+    ``read(y, carry, coefficients)``: the write-back that ``carry`` still owes (X_t <- sum_s mix[s, t] X_s + out[t] y,
+    with the coefficients of the sublayer that produced ``y``), then u = sum_s in[s] X_s with the reading sublayer's
+    ``in``, then u / sqrt(mean(u^2) + eps) * (weight + offset), rounded once to the engine's dtype: one kernel.
+    ``offset`` 1 is a weight stored around zero.  ``forward_add`` is the model's last read: in = 1 (the sum of the
+    streams), chosen rows, nothing stored."""
+    category = "norm"
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.width = int(spec["width"])
+        self.eps = float(spec["eps"])
+        self.offset = float(spec.get("offset", 0.0))
+        self.streams = int(spec.get("streams", 1))
+        if not 1 <= self.streams <= ops.MAX_STREAMS:
+            raise ValueError(f"{self.streams} streams are refused: the kernel takes 1 to {ops.MAX_STREAMS}")
+
+    def param_decls(self):
+        return {"weight": ParamDecl((self.width,), "vector")}
+
+    def bind(self, name, tensor):
+        super().bind(name, tensor)
+        self.params[name] = tensor.to(torch.float32).contiguous()
+
+    def open(self, h):
+        """A carry whose streams begin as copies of ``h`` (float32 [tokens, width])."""
+        streams = torch.empty((h.shape[0], self.streams, self.width), dtype=torch.float32, device=h.device)
+        return StreamCarry(streams, start=h)
+
+    def read(self, y, carry, coefficients, rows=None, store=True):
+        read_in = None if coefficients is None else coefficients[:self.streams]
+        out = ops.stream_step(carry.streams, self.params["weight"], self.offset, self.eps, self.env.dtype,
+                              start=carry.start, y=y if carry.start is None else None,
+                              before=carry.pending if carry.start is None else None, read_in=read_in, rows=rows,
+                              store=store)
+        if store:
+            carry.start, carry.pending = None, None
+        return out
+
+    def forward(self, x, out=None, rows=None):
+        """The norm of a plain float32 [tokens, width] tensor (a model of one layer-less stream)."""
+        carry = self.open(x)
+        return self.read(None, carry, None, rows=rows, store=False)
+
+    def forward_add(self, x, residual, out=None, rows=None, write_residual=True):
+        return self.read(x, residual, None, rows=rows, store=write_residual)
+
+
 register_part("norm", "rms_norm", RMSNorm)
+register_part("norm", "stream_rms_norm", StreamRMSNorm)
 register_part("norm", "scalar_rms_norm", ScalarRMSNorm)

@@ -38,7 +38,9 @@ class RotaryFrequencies(Part):
     """Half-split rotary encoding without a table of positions: only the frequencies
     f_i = theta^(-2i / rot_dim) / scaling_factor, i in [0, rot_dim / 2), as float32 (computed in float64).
     A kernel that rotates forms the angle position * f_i in float and takes its cosine and sine itself, so
-    no longest position has to be known.  ``scaling_factor`` (linear scaling) divides every frequency."""
+    no longest position has to be known.  ``scaling_factor`` (linear scaling) divides every frequency.
+    ``pairing`` says which coordinates frequency i turns: "half_split" (i and i + rot_dim / 2, the default) or
+    "interleaved" (2i and 2i + 1); a mixer's kernel reads it, and a mixer that cannot serve a pairing refuses it."""
     category = "position_encoding"
 
     def __init__(self, spec, env):
@@ -46,6 +48,9 @@ class RotaryFrequencies(Part):
         self.rot_dim = int(spec["rotary_dim"])
         self.theta = float(spec["theta"])
         self.scaling_factor = float(spec.get("scaling_factor", 1.0))
+        self.pairing = str(spec.get("pairing", "half_split"))
+        if self.pairing not in ("half_split", "interleaved"):
+            raise ValueError(f"pairing {self.pairing!r} is refused: half_split or interleaved")
         if self.rot_dim % 2 or self.rot_dim <= 0:
             raise ValueError("rotary_dim must be even and positive")
         i = torch.arange(0, self.rot_dim, 2, dtype=torch.float64)

@@ -3,7 +3,8 @@ from __future__ import annotations
 
 from typing import Callable, Dict
 
-CATEGORIES = ("norm", "position_encoding", "mixer", "feed_forward", "block", "embedding", "head", "token_conv")
+CATEGORIES = ("norm", "position_encoding", "mixer", "feed_forward", "block", "embedding", "head", "token_conv",
+              "stream_mix")
 _PARTS: Dict[str, Dict[str, Callable]] = {c: {} for c in CATEGORIES}
 
 

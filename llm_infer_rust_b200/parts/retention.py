@@ -16,7 +16,11 @@ class DecayRetention(Part):
 
     with S [head_dim, v_head_dim] in float32 in the request's state slot (zeros at a sequence's start); every
     head's o divided by its root mean square (``eps``, no weight), times silu(g), then the output projection.
-    No softmax, no denominator, no bias.  ``decay``: one number per head."""
+    No softmax, no denominator, no bias.  ``decay``: one number per head.
+
+    Two options.  ``qkv_activation`` (silu, ...): q, k and v pass through it right after the projection.
+    ``output`` "joint_norm_sigmoid": instead of the per-head unit norm and silu gate, all heads' o together are
+    RMS-normed with a weight (``norm`` [heads * v_head_dim]) and multiplied by sigmoid(g)."""
     category = "mixer"
 
     def __init__(self, spec, env):
@@ -27,6 +31,12 @@ class DecayRetention(Part):
         self.dv = int(spec["v_head_dim"])
         self.eps = float(spec["eps"])
         self.k_scale = float(spec.get("k_scale", self.d ** -0.5))
+        self.qkv_activation = spec.get("qkv_activation")
+        self.output = str(spec.get("output", "head_unit_silu"))
+        if self.qkv_activation is not None and self.qkv_activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {self.qkv_activation!r} is refused: {sorted(ops.ACTIVATIONS)}")
+        if self.output not in ("head_unit_silu", "joint_norm_sigmoid"):
+            raise ValueError(f"output {self.output!r} is refused: head_unit_silu or joint_norm_sigmoid")
         decay = [float(g) for g in spec["decay"]]
         if len(decay) != self.nh:
             raise ValueError("one decay per head is needed")
@@ -39,8 +49,16 @@ class DecayRetention(Part):
             raise ValueError("the rotation is wider than a head")
 
     def param_decls(self):
-        return {"qkvg_proj": ParamDecl((self.nh * (2 * self.d + 2 * self.dv), self.hidden)),
-                "o_proj": ParamDecl((self.hidden, self.nh * self.dv))}
+        decls = {"qkvg_proj": ParamDecl((self.nh * (2 * self.d + 2 * self.dv), self.hidden)),
+                 "o_proj": ParamDecl((self.hidden, self.nh * self.dv))}
+        if self.output == "joint_norm_sigmoid":
+            decls["norm"] = ParamDecl((self.nh * self.dv,), "vector")
+        return decls
+
+    def bind(self, name, tensor):
+        super().bind(name, tensor)
+        if name == "norm":
+            self.params[name] = tensor.to(torch.float32).contiguous()
 
     def cache_spec(self):
         return None
@@ -52,9 +70,15 @@ class DecayRetention(Part):
         p = self.params
         packed = ops.linear(x, p["qkvg_proj"])
         rope = self.rope
+        gate_column = self.nh * (2 * self.d + self.dv)
+        if self.qkv_activation is not None:
+            ops.activate(packed, self.qkv_activation, columns=gate_column, in_place=True)
         o = ops.retention(packed, cache.state, self.decay, rope.inv_freq if rope else None,
                           rope.rot_dim if rope else 0, self.k_scale, ctx, self.nh, self.d, self.dv)
-        gated = ops.head_unit_norm_gate(o, packed, self.nh * (2 * self.d + self.dv), self.nh, self.dv, self.eps)
+        if self.output == "joint_norm_sigmoid":
+            gated = ops.row_norm_gate(o, p["norm"], packed, gate_column, self.eps)
+        else:
+            gated = ops.head_unit_norm_gate(o, packed, gate_column, self.nh, self.dv, self.eps)
         return ops.linear(gated, p["o_proj"])
 
 

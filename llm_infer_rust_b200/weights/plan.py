@@ -14,8 +14,13 @@ from typing import Optional, Tuple
 class SourceTensor:
     name: str                     # tensor name in the checkpoint
     shape: Tuple[int, ...]
-    init: str = "matrix"          # random-weights rule: "matrix" N(0, std) | "norm" 1 + N(0, norm_std)
+    # random-weights rule: "matrix" N(0, std) | "norm" 1 + N(0, norm_std) | "offset_norm" N(0, norm_std) (a norm
+    # weight stored around zero) | "fill" (every element ``fill``) | "identity" (a square matrix) | "choices" (an
+    # integer table whose rows hold distinct values below ``modulus``)
+    init: str = "matrix"
     integer: bool = False         # an integer table (kept as int32)
+    fill: float = 0.0
+    modulus: int = 0
 
 
 @dataclass(frozen=True)

@@ -94,10 +94,21 @@ def _draw(src, seed: int, std: float, norm_std: float, device) -> torch.Tensor:
         for s in src.shape:
             n *= int(s)
         i = torch.arange(n, dtype=torch.int64, device=device)
-        return (_srl(_mix(key + i), 49)).to(torch.int32).reshape(tuple(src.shape))          # 15 bits
+        drawn = (_srl(_mix(key + i), 49)).to(torch.int32).reshape(tuple(src.shape))          # 15 bits
+        if src.init == "choices":
+            # a row's entries differ: the row's first draw, then its successors, below the modulus
+            step = torch.arange(src.shape[-1], dtype=torch.int32, device=device)
+            drawn = (drawn[..., :1] + step) % int(src.modulus)
+        return drawn
+    if src.init == "fill":
+        return torch.full(tuple(src.shape), float(src.fill), dtype=torch.float32, device=device)
+    if src.init == "identity":
+        return torch.eye(int(src.shape[0]), dtype=torch.float32, device=device)
     z = counter_normal(seed, src.name, src.shape, device)
     if src.init == "norm":
         return 1.0 + norm_std * z if norm_std else torch.ones_like(z)
+    if src.init == "offset_norm":
+        return norm_std * z
     return std * z
 
 
