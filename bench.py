@@ -31,6 +31,9 @@ decoded greedily, and the last K steps are timed.  One JSON line is printed:
 the same width, heads, head size and parameter count, and every kernel of the new design alone beside the like
 kernel of Qwen3's path, each with its share of its roofline (``--design-sizes``, ``--layers``, default 8).
 
+``--design mukenex`` does the same for Mukenex (latent attention over a window with sinks, grouped attention over
+blocks of positions, lightning retention, experts chosen by a table, a residual of four streams).
+
 Peaks come from MEASURED_PEAKS.json beside this file when it is there.  Weights are random
 (drawn on the device), token ids are synthetic.  One GPU only.
 """
@@ -471,18 +474,214 @@ def kernel_table(size, peak):
     return out
 
 
+# ----------------------------------------------------------------------------- --design mukenex
+def mukenex_config(size, layers):
+    """Lightning, latent-attention and block-attention layers in turn over four residual streams.  Routed layers
+    take two of eight experts of half Qwen3's intermediate size (the active parameters of Qwen3's three matrices),
+    dense ones 1.5 x Qwen3's intermediate size in two matrices."""
+    z = DESIGN_SIZES[size]
+    H, G, d, W = z["heads"], z["kv_heads"], z["head_dim"], z["width"]
+    rank = 256 if W <= 1024 else 384
+    moe = {"kind": "moe", "expert": {"ff": z["inter"] // 2}, "router": {"experts": 8, "top": 2}}
+    dense = {"kind": "dense", "ff": z["inter"] * 3 // 2}
+    lightning = {"type": "lightning", "mlp": dense,
+                 "mixer": {"heads": H, "dim": d, "vdim": d,
+                           "decay": [1.0 - 2.0 ** (-5 - 3 * h / max(1, H - 1)) for h in range(H)]}}
+    latent = {"type": "latent_attention", "mlp": moe,
+              "mixer": {"heads": H, "dim": d, "rot_dim": 64, "vdim": d, "kv_rank": rank, "scale": (d + 64) ** -0.5,
+                        "rot": {"base": 1e6, "dims": 64}, "mask": {"size": 1024}}}
+    blocks = {"type": "attention", "mlp": moe,
+              "mixer": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5, "mask": {"size": 1024}}}
+    return {"architecture": "Mukenex", "vocab": z["vocab"], "width": W, "norm": {"eps": 1e-5}, "streams": 4,
+            "logit_softcap": 30.0, "layers": [(lightning, latent, blocks)[i % 3] for i in range(layers)]}
+
+
+def mukenex_kernel_table(size, peak):
+    """Every kernel of Mukenex alone, beside the like kernel of Qwen3's path, at one layer's sizes: a prompt portion of
+    2,048 tokens and a decode step of 8 rows at 2,048 tokens (``frac`` as in ``kernel_table``)."""
+    import types
+    import torch
+    from llm_infer_rust_b200.kernels import ops
+    from llm_infer_rust_b200.parts.attention import decode_splits
+    z = DESIGN_SIZES[size]
+    W, nh, nkv, d, I = z["width"], z["heads"], z["kv_heads"], z["head_dim"], z["inter"]
+    rank, r, S, E, top, ffe, window = (256 if W <= 1024 else 384), 64, 4, 8, 2, z["inter"] // 2, 1024
+    dev, bf = torch.device("cuda"), torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    page, ctx_len, rows_dec = 16, 2048, 8
+    out = {}
+
+    def put(name, us, nbytes=None, flops=None, of="hbm"):
+        rec = {"us": round(us, 2)}
+        if nbytes is not None:
+            rec["gb_s"] = round(nbytes / us / 1e3, 1)
+            rec["frac"] = round(nbytes / us / 1e3 / peak["hbm_gbs"], 3)
+        if flops is not None:
+            top_ = {"bf16": peak["bf16_tflops"], "fp32": peak["fp32_tflops"]}[of]
+            rec["tflops"] = round(flops / us / 1e6, 2)
+            rec["frac"] = round(flops / us / 1e6 / top_, 3)
+            rec["of"] = of
+        out[name] = rec
+
+    def step(rows):
+        cu, pos = [0], []
+        for prefix, n in rows:
+            cu.append(cu[-1] + n)
+            pos += list(range(prefix, prefix + n))
+        R = len(rows)
+        width = -(-max(p + n for p, n in rows) // page)
+        table = torch.arange(1, R * width + 1, dtype=torch.int32, device=dev).view(R, width).contiguous()
+        slots = [int(table[r_, (p + i) // page]) * page + (p + i) % page for r_, (p, n) in enumerate(rows) for i in range(n)]
+        return types.SimpleNamespace(
+            num_rows=R, cu_q=i32(cu), positions=i32(pos), prefix_len=i32([p for p, _ in rows]),
+            kv_len=i32([p + n for p, n in rows]), state_slots=i32(list(range(1, R + 1))), slots=i32(slots), table=table,
+            rows=i32(list(range(R))), tokens=cu[-1], pages=R * width + 1, max_q_len=max(n for _, n in rows),
+            num_prefill=sum(n > 1 for _, n in rows))
+
+    def seen(T, size_, blocks):         # (query, key) pairs of a prompt of T tokens under a window or blocks of size_
+        return sum((p % size_ if blocks else min(p, size_ - 1)) + 1 for p in range(T))
+
+    for phase, c in (("prefill", step([(0, ctx_len)])), ("decode", step([(ctx_len - 1, 1)] * rows_dec))):
+        T = c.tokens
+        # --- the residual: write-back of one sublayer, read and norm of the next
+        streams = torch.randn(T, S, W, device=dev)
+        y = torch.randn(T, W, device=dev).to(bf)
+        coef = torch.rand(S * (S + 2), device=dev)
+        wn = torch.zeros(W, device=dev)
+        put(f"{phase}.mukenex.stream_step", timed_alone(lambda: ops.stream_step(
+            streams, wn, 1.0, 1e-5, bf, y=y, before=coef, read_in=coef[:S]), flush), T * W * (8 * S + 4))
+        res_b, xb = torch.randn(T, W, device=dev).to(bf), torch.randn(T, W, device=dev).to(bf)
+        wb = torch.ones(W, dtype=bf, device=dev)
+        put(f"{phase}.qwen3.add_rms_norm", timed_alone(lambda: ops.add_rms_norm(xb, res_b, wb, 1e-6), flush), T * W * 8)
+        # --- between the projection and attention
+        cq = (nh + 2 * nkv) * d
+        packed = (torch.randn(T, cq, device=dev) * 0.5).to(bf)
+        k_cache = torch.zeros(c.pages, nkv, page, d, dtype=bf, device=dev).normal_()
+        v_cache = torch.zeros(c.pages, nkv, page, d, dtype=bf, device=dev).normal_()
+        q = torch.empty(T, nh * d, dtype=bf, device=dev)
+        bias, hw = torch.zeros(cq, device=dev), torch.ones(d, device=dev)
+        put(f"{phase}.mukenex.heads_prepare", timed_alone(lambda: ops.heads_prepare(
+            packed, q, k_cache, v_cache, c.positions, c.slots, nh, nkv, d, d, bias=bias, q_weight=hw, k_weight=hw,
+            eps=1e-5), flush), T * cq * 4)
+        cos, sin = torch.ones(4096, d // 2, device=dev), torch.zeros(4096, d // 2, device=dev)
+        hn = torch.ones(d, dtype=bf, device=dev)
+        put(f"{phase}.qwen3.qkv_post", timed_alone(lambda: ops.qkv_post(
+            packed, q, k_cache, v_cache, hn, hn, 1e-6, cos, sin, d, c.positions, c.slots, nh, nkv, d), flush), T * cq * 4)
+        lq = nh * (d + r)
+        lpacked = (torch.randn(T, lq + rank + r, device=dev) * 0.5).to(bf)
+        lk = torch.zeros(c.pages, 1, page, rank + r, dtype=bf, device=dev).normal_()
+        lv = torch.zeros(c.pages, 1, page, rank, dtype=bf, device=dev).normal_()
+        uk_t = (torch.randn(nh, rank, d, device=dev) * d ** -0.5).to(bf)
+        uv = (torch.randn(nh, d, rank, device=dev) * rank ** -0.5).to(bf)
+        q_plain = lpacked[:, :lq].view(T, nh, d + r)[:, :, :d].transpose(0, 1)
+        q_lat = ops.head_products(q_plain, uk_t)
+        put(f"{phase}.mukenex.head_products_uk", timed_alone(lambda: ops.head_products(q_plain, uk_t), flush),
+            flops=2.0 * T * nh * d * rank, of="bf16")
+        lqo = torch.empty(T, nh * (rank + r), dtype=bf, device=dev)
+        inv_freq = torch.pow(torch.tensor(1e6), -torch.arange(0, r, 2) / r).to(dev)
+        lw = torch.ones(rank, device=dev)
+        put(f"{phase}.mukenex.latent_prepare", timed_alone(lambda: ops.latent_prepare(
+            lpacked, q_lat, lqo, lk, lv, lw, 1e-5, c.positions, c.slots, nh, d, r, rank, inv_freq=inv_freq, rot_dims=r),
+            flush), T * (nh * (rank * 2 + r * 2) * 2 + (rank + r) * 2 * 2))
+        # --- attention
+        o = torch.empty(T, nh * d, dtype=bf, device=dev)
+        lo = torch.empty(T, nh * rank, dtype=bf, device=dev)
+        sinks = torch.zeros(nh, device=dev)
+        if phase == "prefill":
+            put("prefill.mukenex.attention_blocks", timed_alone(lambda: ops.prefill_attention(
+                q, k_cache, v_cache, o, c.table, c.cu_q, c.kv_len, c.prefix_len, c.rows, 1, T, nh, nkv, d, page, None,
+                d ** -0.5, v_head_dim=d, precise_weights=True, chunk=window), flush, repeats=3),
+                flops=4.0 * nh * d * seen(T, window, True), of="bf16")
+            put("prefill.mukenex.attention_latent", timed_alone(lambda: ops.prefill_attention(
+                lqo, lk, lv, lo, c.table, c.cu_q, c.kv_len, c.prefix_len, c.rows, 1, T, nh, 1, rank + r, page, window,
+                (d + r) ** -0.5, v_head_dim=rank, precise_weights=True, sinks=sinks), flush, repeats=3),
+                flops=2.0 * nh * (2 * rank + r) * seen(T, window, False), of="bf16")
+            put("prefill.qwen3.attention", timed_alone(lambda: ops.prefill_attention(
+                q, k_cache, v_cache, o, c.table, c.cu_q, c.kv_len, c.prefix_len, c.rows, 1, T, nh, nkv, d, page, None,
+                d ** -0.5), flush), flops=4.0 * nh * d * T * (T + 1) / 2, of="bf16")
+        else:
+            def decode(name, qq, kk, vv, oo, heads, kvh, dk, dv_, bound, nbytes, **kw):
+                plain = dk == dv_
+                splits = decode_splits(ops.decode_ctas_per_split(bf, rows_dec, heads, kvh, dk, page, plain), bound, 148)
+                need = ops.decode_scratch_floats(rows_dec, heads, max(dk, dv_), splits)
+                scratch = torch.empty(max(need, 1), device=dev)
+                win, scale = kw.pop("window_", None), kw.pop("scale_", dk ** -0.5)
+                put(name, timed_alone(lambda: ops.decode_attention(
+                    qq, kk, vv, oo, scratch, c.table, c.cu_q, c.kv_len, c.rows, rows_dec, heads, kvh, dk, page,
+                    win, scale, splits, **kw), flush), nbytes)
+            kv_all = rows_dec * ctx_len * nkv * d * 2 * 2
+            decode("decode.mukenex.attention_blocks", q, k_cache, v_cache, o, nh, nkv, d, d, window,
+                   rows_dec * window * nkv * d * 2 * 2, v_head_dim=d, precise_weights=True, chunk=window)
+            decode("decode.mukenex.attention_latent", lqo, lk, lv, lo, nh, 1, rank + r, rank, window,
+                   rows_dec * window * (2 * rank + r) * 2, v_head_dim=rank, precise_weights=True, sinks=sinks,
+                   window_=window)
+            decode("decode.qwen3.attention", q, k_cache, v_cache, o, nh, nkv, d, d, ctx_len, kv_all)
+        lo_t = lo.view(T, nh, rank).transpose(0, 1)
+        lout = torch.empty(T, nh * d, dtype=bf, device=dev)
+        put(f"{phase}.mukenex.head_products_uv", timed_alone(lambda: ops.head_products(
+            lo_t, uv, out=lout.view(T, nh, d).transpose(0, 1)), flush), flops=2.0 * T * nh * d * rank, of="bf16")
+        # --- gates and activations
+        gp = (torch.randn(T, 2 * nh * d, device=dev)).to(bf)
+        put(f"{phase}.mukenex.sigmoid_gate_mul", timed_alone(lambda: ops.sigmoid_gate_mul(o, gp, nh * d), flush), T * nh * d * 6)
+        zf = torch.randn(T, I * 3 // 2, device=dev).to(bf)
+        put(f"{phase}.mukenex.gelu", timed_alone(lambda: ops.activate(zf, "gelu_erf", in_place=True), flush), T * I * 3 // 2 * 4)
+        gu = torch.randn(T, 2 * I, device=dev).to(bf)
+        put(f"{phase}.qwen3.silu_mul", timed_alone(lambda: ops.silu_mul(gu), flush), T * I * 6)
+        # --- lightning: activation of q, k, v, the recurrence, the joint norm with its gate
+        rp = (torch.randn(T, nh * 4 * d, device=dev) * 0.3).to(bf)
+        put(f"{phase}.mukenex.silu_qkv", timed_alone(lambda: ops.activate(rp, "silu", columns=nh * 3 * d, in_place=True),
+                                                     flush), T * nh * 3 * d * 4)
+        rstate = torch.zeros(rows_dec + 1, nh, d, d, device=dev)
+        decay = torch.full((nh,), 0.99, device=dev)
+        us = timed_alone(lambda: ops.retention(rp, rstate, decay, None, 0, 1.0, c, nh, d, d), flush,
+                         repeats=3 if phase == "prefill" else 7)
+        if phase == "prefill":
+            put("prefill.mukenex.retention", us, flops=4.0 * T * nh * d * d, of="fp32")
+        else:
+            put("decode.mukenex.retention", us, rows_dec * nh * d * d * 8)
+        ro = torch.randn(T, nh * d, device=dev)
+        nw = torch.ones(nh * d, device=dev)
+        put(f"{phase}.mukenex.row_norm_gate", timed_alone(lambda: ops.row_norm_gate(ro, nw, rp, nh * 3 * d, 1e-5), flush),
+            T * nh * d * 8)
+        # --- experts beside Qwen3's feed-forward with the same active parameters
+        xe = torch.randn(T, W, device=dev).to(bf)
+        ids = torch.randint(0, 4096, (T,), device=dev, dtype=torch.int32)
+        table = torch.stack([torch.randperm(E)[:top] for _ in range(4096)]).to(torch.int32).to(dev)
+        gate_up = (torch.randn(E, 2 * ffe, W, device=dev) * W ** -0.5).to(bf)
+        down = (torch.randn(E, W, ffe, device=dev) * ffe ** -0.5).to(bf)
+        fl = 6.0 * T * top * W * ffe
+        us = timed_alone(lambda: ops.table_experts(xe, ids, table, gate_up, down), flush)
+        if phase == "prefill":
+            put("prefill.mukenex.table_experts", us, flops=fl, of="bf16")
+        else:
+            put("decode.mukenex.table_experts", us, min(E, T * top) * 3 * W * ffe * 2)
+        wgu = (torch.randn(2 * I, W, device=dev) * W ** -0.5).to(bf)
+        wdn = (torch.randn(W, I, device=dev) * I ** -0.5).to(bf)
+        us = timed_alone(lambda: ops.linear(ops.silu_mul(ops.linear(xe, wgu)), wdn), flush)
+        if phase == "prefill":
+            put("prefill.qwen3.feed_forward", us, flops=6.0 * T * W * I, of="bf16")
+        else:
+            put("decode.qwen3.feed_forward", us, 3 * W * I * 2)
+    return out
+
+
+DESIGNS = {"kefetar": (kefetar_config, kernel_table), "mukenex": (mukenex_config, mukenex_kernel_table)}
+
+
 def design_main(args) -> int:
     import torch
     peak, peak_source = peaks()
     # float32 FMA throughput of the device: SMs x 128 lanes x 2 x the highest SM clock
     props = torch.cuda.get_device_properties(0)
     peak["fp32_tflops"] = props.multi_processor_count * 128 * 2 * 1.965e9 / 1e12
-    context, line = args.context, {"design": "kefetar", "layers": args.layers or 8, "context": args.context,
+    make_config, make_table = DESIGNS[args.design]
+    context, line = args.context, {"design": args.design, "layers": args.layers or 8, "context": args.context,
                                    "dtype": "bf16", "data": "synthetic token ids, random weights", "peaks": peak_source,
                                    "sizes": {}, "kernels": {}}
     for size in [n for n in args.design_sizes.split(",") if n]:
         rec = {}
-        for name, raw in (("kefetar", kefetar_config(size, args.layers or 8)), ("qwen3", qwen3_config(size, args.layers or 8))):
+        for name, raw in ((args.design, make_config(size, args.layers or 8)), ("qwen3", qwen3_config(size, args.layers or 8))):
             engine = design_engine(raw, 8, context)
             vocab = raw.get("vocab", raw.get("vocab_size"))
             ms = prefill_timed(engine, 2048, vocab)
@@ -498,7 +697,7 @@ def design_main(args) -> int:
             release()
         line["sizes"][size] = rec
         if not args.no_kernels:
-            line["kernels"][size] = kernel_table(size, peak)
+            line["kernels"][size] = make_table(size, peak)
             release()
     print(json.dumps(line))
     return 0
@@ -519,12 +718,12 @@ def main() -> int:
                     help="other shapes measured into `points` (decode at batch 1 / 8 / 64, prefill), comma separated")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one phase alone and print a short line (for profiling)")
-    ap.add_argument("--design", choices=["qwen3", "kefetar"], default="qwen3",
-                    help="kefetar: the new design beside Qwen3 at equal sizes, and its kernels alone (another line)")
-    ap.add_argument("--design-sizes", default="1k,4k", help="layer sizes of --design kefetar, comma separated")
-    ap.add_argument("--no-kernels", action="store_true", help="--design kefetar without the table of single kernels")
+    ap.add_argument("--design", choices=["qwen3", "kefetar", "mukenex"], default="qwen3",
+                    help="kefetar, mukenex: that design beside Qwen3 at equal sizes, and its kernels alone (another line)")
+    ap.add_argument("--design-sizes", default="1k,4k", help="layer sizes of --design kefetar / mukenex, comma separated")
+    ap.add_argument("--no-kernels", action="store_true", help="--design ... without the table of single kernels")
     args = ap.parse_args()
-    if args.design == "kefetar" and args.impl == "ours":
+    if args.design in DESIGNS and args.impl == "ours":
         if args.gpus != 1:
             print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
             return 2

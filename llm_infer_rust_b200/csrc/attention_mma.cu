@@ -72,10 +72,18 @@ __device__ __forceinline__ float fast_exp2(float x) {      // 2^x in one special
 // cap_log2 * tanh(score * tanh_in) (cap_log2 = cap * log2(e), tanh_in = scale / cap; cap_log2 <= 0: no cap).
 // split_p: the weights enter P.V as two bfloat16 terms, the rounded weight and what the rounding left, so that
 // the product carries the weights to about 16 bits instead of 8.
+// chunk C > 0: a query at position p also sees only keys from p - p % C on (its own block of C positions, counted
+// from the sequence's start).  sinks (one float per query head, or null): exp(sink) joins the softmax's denominator.
 struct ScoreForm {
   float scale_log2, tanh_in, cap_log2;
   int split_p;
+  int chunk;
+  const float* sinks;
 };
+// The sum of a row's weights with the sink's term (the row's maximum m is in log2 units).
+__device__ __forceinline__ float with_sink(const ScoreForm& sf, int head, float m, float l) {
+  return (sf.sinks != nullptr && l > 0.0f) ? l + exp2f(sf.sinks[head] * 1.4426950408889634f - m) : l;
+}
 __device__ __forceinline__ float tanh_by_exp2(float x) {     // 1 - 2 / (e^(2x) + 1): absolute error about 1e-7
   float e;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(e) : "f"(x * 2.8853900817779268f));
@@ -186,8 +194,10 @@ __device__ __forceinline__ void block_mma(const bf16* qs, const unsigned char* k
       if (MASKED) {
         const int key = first_key + n * 8 + t2 + e;
         const bool in_seq = key < kv_end;
-        v0 = in_seq && v0 && key <= qpos0 && (window <= 0 || key > qpos0 - window);
-        v1 = in_seq && v1 && key <= qpos1 && (window <= 0 || key > qpos1 - window);
+        v0 = in_seq && v0 && key <= qpos0 && (window <= 0 || key > qpos0 - window) &&
+             (sf.chunk <= 0 || key >= qpos0 - qpos0 % sf.chunk);
+        v1 = in_seq && v1 && key <= qpos1 && (window <= 0 || key > qpos1 - window) &&
+             (sf.chunk <= 0 || key >= qpos1 - qpos1 % sf.chunk);
       }
       float a0 = s[n][e] * sf.scale_log2, a1 = s[n][2 + e] * sf.scale_log2;
       if (SHAPED && sf.cap_log2 > 0.0f) {
@@ -282,6 +292,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
   const int kv_end = kv_len[row];
   const int qp = kv_end - 1;
   int k_begin = window > 0 ? max(0, qp - window + 1) : 0;
+  if (sf.chunk > 0) k_begin = max(k_begin, qp - qp % sf.chunk);
   k_begin -= k_begin % KB;
   const int blocks_total = (kv_end - k_begin + KB - 1) / KB;
   const int per_split = (blocks_total + splits - 1) / splits;
@@ -349,7 +360,8 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
       for (int c = 0; c < NB * 8; ++c) *reinterpret_cast<uint4*>(t + NB * HALF_BYTES + (c >> 3) * HALF_BYTES + lane * 128 + (c & 7) * 16) = zero;
     }
     __syncwarp();
-    if (first_key + KB <= kv_end && (window <= 0 || first_key > qp - window))
+    if (first_key + KB <= kv_end && (window <= 0 || first_key > qp - window) &&
+        (sf.chunk <= 0 || first_key >= qp - qp % sf.chunk))
       block_mma<false, SHAPED>(qs, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos0, qpos1, sf, st);
     else
       block_mma<true, SHAPED>(qs, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos0, qpos1, sf, st);
@@ -395,6 +407,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     }
     const int head = head0 + r;
     if (splits == 1) {
+      l = with_sink(sf, head, m, l);
       out[(static_cast<size_t>(tok) * nh + head) * D + dim] = __float2bfloat16_rn(l > 0.0f ? o / l : 0.0f);
     } else if (cluster_merge) {
       mine[r * MS + dim] = o;                          // this CTA's part, for the cluster's first CTA to read
@@ -423,6 +436,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
           l += src[D + 1] * f;
           o += src[dim] * f;
         }
+        l = with_sink(sf, head0 + r, m, l);
       }
       out[(static_cast<size_t>(tok) * nh + head0 + r) * D + dim] = __float2bfloat16_rn(l > 0.0f ? o / l : 0.0f);
     }
@@ -433,7 +447,8 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
 // grid (decode rows, nh): combines the splits of one head (maxima are in log2 units).
 __global__ void decode_mma_merge_kernel(bf16* __restrict__ out, const float* __restrict__ part_acc,
                                         const float* __restrict__ part_ml, const int* __restrict__ cu_q,
-                                        const int* __restrict__ rows, int nh, int splits) {
+                                        const int* __restrict__ rows, int nh, int splits,
+                                        const float* __restrict__ sinks) {
   pdl_launch_dependents();
   pdl_wait();
   const int head = blockIdx.y;
@@ -449,6 +464,7 @@ __global__ void decode_mma_merge_kernel(bf16* __restrict__ out, const float* __r
         l += part_ml[(base + s) * 2 + 1] * f;
         o += part_acc[(base + s) * D + dim] * f;
       }
+      if (sinks != nullptr && l > 0.0f) l += exp2f(sinks[head] * 1.4426950408889634f - m);
     }
     out[(static_cast<size_t>(tok) * nh + head) * D + dim] = __float2bfloat16_rn(l > 0.0f ? o / l : 0.0f);
   }
@@ -499,6 +515,7 @@ prefill_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
   const int kv_end = min(kv_len[row], prefix + tok0 + ntok);     // causal: nothing later is visible to this tile
   const int p_lo = prefix + tok0;
   int k_begin = window > 0 ? max(0, p_lo - window + 1) : 0;
+  if (sf.chunk > 0) k_begin = max(k_begin, p_lo - p_lo % sf.chunk);
   k_begin -= k_begin % KB;
   const int nblk = (kv_end - k_begin + KB - 1) / KB;
   const int* table = block_table + static_cast<size_t>(row) * table_stride;
@@ -532,7 +549,8 @@ prefill_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
   const int w_tok_lo = warp * tokens_per_warp;
   const int w_tok_hi = min(ntok, w_tok_lo + tokens_per_warp) - 1;           // < w_tok_lo: the warp holds no token
   const int w_p_hi = p_lo + w_tok_hi;
-  const int w_first_key = window > 0 ? max(0, p_lo + w_tok_lo - window + 1) : 0;
+  int w_first_key = window > 0 ? max(0, p_lo + w_tok_lo - window + 1) : 0;
+  if (sf.chunk > 0) w_first_key = max(w_first_key, (p_lo + w_tok_lo) - (p_lo + w_tok_lo) % sf.chunk);
 
   WarpAcc st;
   st.init();
@@ -578,7 +596,8 @@ prefill_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
     if (w_tok_hi >= w_tok_lo && first_key <= w_p_hi && first_key + KB > w_first_key) {
       // All keys of the block lie at or before the warp's first query (and inside its last query's window)?
       const bool all_visible = first_key + KB - 1 <= p_lo + w_tok_lo && first_key + KB <= kv_end &&
-                               (window <= 0 || first_key > w_p_hi - window);
+                               (window <= 0 || first_key > w_p_hi - window) &&
+                               (sf.chunk <= 0 || first_key >= w_p_hi - w_p_hi % sf.chunk);
       if (all_visible)
         block_mma<false, SHAPED>(my_q, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos[0], qpos[1], sf, st);
       else
@@ -600,7 +619,8 @@ prefill_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
     if (tok_of[h] < 0) continue;
     const int head = head0 + (g + 8 * h) % group;
     bf16* dst = out + (static_cast<size_t>(q_begin + tok0 + tok_of[h]) * nh + head) * D;
-    const float inv = st.l[h] > 0.0f ? 1.0f / st.l[h] : 0.0f;
+    const float l = with_sink(sf, head, st.m[h], st.l[h]);
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
 #pragma unroll
     for (int dn = 0; dn < D / 8; ++dn)
       *reinterpret_cast<uint32_t*>(dst + dn * 8 + t2) = pack_bf16(st.o[dn][2 * h] * inv, st.o[dn][2 * h + 1] * inv);
@@ -655,12 +675,14 @@ B200_EXPORT int b200_kv_tensor_map(void* out_map, const void* cache, long long r
   return 0;
 }
 
-static ScoreForm score_form(float scale, float softcap, int split_p) {
+static ScoreForm score_form(float scale, float softcap, int split_p, int chunk, const float* sinks) {
   ScoreForm sf;
   sf.scale_log2 = scale * 1.4426950408889634f;
   sf.tanh_in = softcap > 0.0f ? scale / softcap : 0.0f;
   sf.cap_log2 = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f;
   sf.split_p = split_p;
+  sf.chunk = chunk;
+  sf.sinks = sinks;
   return sf;
 }
 
@@ -671,7 +693,8 @@ B200_EXPORT int b200_decode_attention_mma(const void* q, const void* k_map, cons
                                           float* scratch, const int* block_table, int table_stride,
                                           const int* cu_q, const int* kv_len, const int* rows, int n_rows, int nh,
                                           int nkv, int page_size, int window, float scale, int splits,
-                                          float softcap, int split_p, int* err, cudaStream_t stream) {
+                                          float softcap, int split_p, int chunk, const float* sinks, int* err,
+                                          cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || nh / nkv > QROWS || page_size <= 0 || splits <= 0) return B200_BAD_SIZE;
   if ((page_size & (page_size - 1)) != 0) return B200_BAD_SIZE;
@@ -708,11 +731,11 @@ B200_EXPORT int b200_decode_attention_mma(const void* q, const void* k_map, cons
   int rc = b200_launch(kernel, grid, dim3(kWarps * 32), smem, stream, cluster_merge ? splits : 0,
                        kmap, vmap, static_cast<const bf16*>(q), static_cast<bf16*>(out), part_acc, part_ml, block_table,
                        table_stride, cu_q, kv_len, rows, nh, nkv, page_size, box_rows, window,
-                       score_form(scale, softcap, split_p), cluster_merge ? 1 : 0, err);
+                       score_form(scale, softcap, split_p, chunk, sinks), cluster_merge ? 1 : 0, err);
   if (rc != 0 || splits == 1 || cluster_merge) return rc;
   dim3 mgrid(n_rows, nh);
   return b200_launch(decode_mma_merge_kernel, mgrid, dim3(D >= 128 ? 128 : 64), 0, stream, 0, static_cast<bf16*>(out),
-                     static_cast<const float*>(part_acc), static_cast<const float*>(part_ml), cu_q, rows, nh, splits);
+                     static_cast<const float*>(part_acc), static_cast<const float*>(part_ml), cu_q, rows, nh, splits, sinks);
 }
 
 constexpr size_t kPfQBytes = PF_ROWS * LD * sizeof(bf16);
@@ -726,7 +749,8 @@ B200_EXPORT int b200_prefill_attention_mma(const void* q, const void* k_map, con
                                            const int* block_table, int table_stride, const int* cu_q,
                                            const int* kv_len, const int* prefix_len, const int* rows, int n_rows,
                                            int max_q_len, int nh, int nkv, int page_size, int window, float scale,
-                                           float softcap, int split_p, int* err, cudaStream_t stream) {
+                                           float softcap, int split_p, int chunk, const float* sinks, int* err,
+                                          cudaStream_t stream) {
   if (n_rows <= 0 || max_q_len <= 0) return 0;
   if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || nh / nkv > QROWS || page_size <= 0) return B200_BAD_SIZE;
   if ((page_size & (page_size - 1)) != 0) return B200_BAD_SIZE;
@@ -749,6 +773,6 @@ B200_EXPORT int b200_prefill_attention_mma(const void* q, const void* k_map, con
   dim3 grid(nkv, n_rows, n_tiles);
   kernel<<<grid, PF_WARPS * 32, smem, stream>>>(
       kmap, vmap, static_cast<const bf16*>(q), static_cast<bf16*>(out), block_table, table_stride, cu_q, kv_len,
-      prefix_len, rows, nh, nkv, page_size, box_rows, window, score_form(scale, softcap, split_p), err);
+      prefix_len, rows, nh, nkv, page_size, box_rows, window, score_form(scale, softcap, split_p, chunk, sinks), err);
   return b200_check_launch();
 }

@@ -26,7 +26,7 @@ __global__ void __launch_bounds__(1024)
 expert_route_kernel(const int* __restrict__ token_ids, const int* __restrict__ table, int vocab, int top, int experts,
                     int tokens, int* __restrict__ sorted_token, int* __restrict__ pos_of_pair,
                     int* __restrict__ expert_start, int* __restrict__ tile_expert, int* __restrict__ tile_first,
-                    int* __restrict__ num_tiles, int* err) {
+                    int* __restrict__ num_tiles, int tile_rows, int* err) {
   extern __shared__ int sm[];
   int* count = sm;                    // [experts]
   int* start = sm + experts;          // [experts + 1]
@@ -45,7 +45,7 @@ expert_route_kernel(const int* __restrict__ token_ids, const int* __restrict__ t
     for (int e = 0; e < experts; ++e) {
       start[e] = at;
       expert_start[e] = at;
-      for (int r = at; r < at + count[e]; r += TM) { tile_expert[n] = e; tile_first[n] = r; ++n; }
+      for (int r = at; r < at + count[e]; r += tile_rows) { tile_expert[n] = e; tile_first[n] = r; ++n; }
       at += count[e];
     }
     start[experts] = at;
@@ -245,11 +245,28 @@ expert_combine_kernel(float* __restrict__ out, const float* __restrict__ Y, cons
 }
 
 // ------------------------------------------------------------------ C interface
-// Ints of scratch that the routing needs for (tokens, top, experts).
+// Ints of scratch that the routing needs for (tokens, top, experts); row tiles of at least 64 rows.
 B200_EXPORT long long b200_expert_route_ints(int tokens, int top, int experts) {
   const long long pairs = static_cast<long long>(tokens) * top;
   const long long tiles = (pairs + TM - 1) / TM + experts;
   return 2 * pairs + (experts + 1) + 2 * tiles + 1;
+}
+
+// Where the parts of the routing scratch lie.
+struct RouteLayout {
+  int *sorted_token, *pos_of_pair, *expert_start, *tile_expert, *tile_first, *num_tiles;
+  int tiles;
+};
+static RouteLayout route_layout(int* route, int pairs, int experts) {
+  RouteLayout r;
+  r.tiles = (pairs + TM - 1) / TM + experts;
+  r.sorted_token = route;
+  r.pos_of_pair = r.sorted_token + pairs;
+  r.expert_start = r.pos_of_pair + pairs;
+  r.tile_expert = r.expert_start + experts + 1;
+  r.tile_first = r.tile_expert + r.tiles;
+  r.num_tiles = r.tile_first + r.tiles;
+  return r;
 }
 
 // x [tokens, width] -> out [tokens, width] float32.  `h` holds pairs * ff elements of x's dtype, `y` pairs * width
@@ -262,17 +279,14 @@ B200_EXPORT int b200_table_experts(const void* x, int dtype, const int* token_id
   const long long pairs_ll = static_cast<long long>(tokens) * top;
   if (pairs_ll > (1ll << 30) || (2 * experts + 1) * sizeof(int) > 48 * 1024) return B200_BAD_SIZE;
   const int pairs = static_cast<int>(pairs_ll);
-  const int tiles = (pairs + TM - 1) / TM + experts;
+  const RouteLayout rl = route_layout(route, pairs, experts);
+  const int tiles = rl.tiles;
   if (tiles > 65535) return B200_BAD_SIZE;
-  int* sorted_token = route;
-  int* pos_of_pair = sorted_token + pairs;
-  int* expert_start = pos_of_pair + pairs;
-  int* tile_expert = expert_start + experts + 1;
-  int* tile_first = tile_expert + tiles;
-  int* num_tiles = tile_first + tiles;
+  int *sorted_token = rl.sorted_token, *pos_of_pair = rl.pos_of_pair, *expert_start = rl.expert_start;
+  int *tile_expert = rl.tile_expert, *tile_first = rl.tile_first, *num_tiles = rl.num_tiles;
   expert_route_kernel<<<1, 1024, (2 * experts + 1) * sizeof(int), stream>>>(
       token_ids, table, vocab, top, experts, tokens, sorted_token, pos_of_pair, expert_start, tile_expert, tile_first,
-      num_tiles, err);
+      num_tiles, TM, err);
   int rc = b200_check_launch();
   if (rc != 0) return rc;
   const dim3 g1((ff + TN - 1) / TN, tiles), g2((width + TN - 1) / TN, tiles);

@@ -303,7 +303,7 @@ def prefill_attention(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefi
 
     ``chunk`` C: a query at position p sees only keys from p - p % C on (its own block of C positions, counted from
     the sequence's start); ``sinks`` (float32, one per query head): exp(sink) joins the softmax's denominator.  Both
-    take the all-sizes kernel.
+    are served by the mma.sync and the all-sizes kernels, not by the tcgen05 one.
 
     ``tiles_per_cta`` (head size 128 on the tcgen05 kernel only): 1 or 2 tiles of 128 query vectors per
     CTA, 0 lets the kernel's launcher choose by the size of the grid."""
@@ -317,12 +317,13 @@ def prefill_attention(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefi
     cap = float(softcap or 0.0)
     _check_sinks(sinks, num_heads)
     plain_mask = not chunk and sinks is None
-    if plain_mask and dv == head_dim and decode_uses_tensor_cores(q.dtype, num_heads, num_kv_heads, head_dim, page_size):
+    if dv == head_dim and decode_uses_tensor_cores(q.dtype, num_heads, num_kv_heads, head_dim, page_size):
         if k_cache.shape[1] != num_kv_heads or k_cache.shape[2] != page_size:
             raise KernelError("the cache must be [pages + 1, kv_heads, page_size, head_dim]")
         box_rows = min(page_size, 32)
         group = num_heads // num_kv_heads
-        if head_dim == 128 and 128 % group == 0 and max_q_len * group >= 128 and not cap > 0.0 and not precise_weights:
+        if head_dim == 128 and 128 % group == 0 and max_q_len * group >= 128 and not cap > 0.0 and not precise_weights \
+                and plain_mask:
             # head size 128 and at least one full tile of 128 query vectors: the tcgen05 kernel
             rc = load_cuda_library("attention_tcgen05.cu").b200_prefill_attention_tcgen05(
                 _p(q), kv_tensor_map(k_cache, box_rows), kv_tensor_map(v_cache, box_rows), _p(out), _p(block_table),
@@ -335,7 +336,7 @@ def prefill_attention(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefi
             _p(q), kv_tensor_map(k_cache, box_rows), kv_tensor_map(v_cache, box_rows), _p(out), _p(block_table),
             block_table.shape[-1], _p(cu_q), _p(kv_len), _p(prefix_len), _p(rows), n_rows, max_q_len, num_heads,
             num_kv_heads, page_size, int(window or 0), ctypes.c_float(scale), ctypes.c_float(cap),
-            int(bool(precise_weights)), _p(error_word(q.device)), _stream())
+            int(bool(precise_weights)), int(chunk or 0), _p(sinks), _p(error_word(q.device)), _stream())
         _ok(rc, "prefill_attention_mma")
         return
     rc = _attention(max(head_dim, dv)).b200_prefill_attention(
@@ -417,7 +418,7 @@ def decode_attention(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_le
     if k_cache.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelError("q, cache and output must share a dtype")
     dv = int(v_head_dim or head_dim)
-    plain = dv == head_dim and not chunk and sinks is None
+    plain = dv == head_dim
     need = decode_scratch_floats(n_rows, num_heads, max(head_dim, dv), splits)
     if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
         raise KernelError(f"decode attention needs {need} floats of scratch")
@@ -429,7 +430,7 @@ def decode_attention(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_le
             _p(q), kv_tensor_map(k_cache, box_rows), kv_tensor_map(v_cache, box_rows), _p(out), _p(scratch), _p(block_table), block_table.shape[-1],
             _p(cu_q), _p(kv_len), _p(rows), n_rows, num_heads, num_kv_heads, page_size, int(window or 0),
             ctypes.c_float(scale), splits, ctypes.c_float(softcap or 0.0), int(bool(precise_weights)),
-            _p(error_word(q.device)), _stream())
+            int(chunk or 0), _p(sinks), _p(error_word(q.device)), _stream())
         in_kernel = splits == 1 or (splits in (2, 4, 8) and splits * num_kv_heads * n_rows <= _sm_count(q.device))
         _ok(rc, "decode_attention_mma", 1 if in_kernel else 2)      # (a cluster of 2, 4 or 8 splits combines them itself)
         return
@@ -1667,10 +1668,15 @@ def latent_prepare(x: torch.Tensor, q_lat: torch.Tensor, q_out: torch.Tensor, k_
 
 
 # --------------------------------------------------------------------------- experts chosen by a table
+EXPERTS_TCGEN05_FROM_PAIRS = 512      # steps with this many (token, expert) pairs take the tcgen05 products
+
+
 def table_experts(x: torch.Tensor, token_ids: torch.Tensor, table: torch.Tensor, gate_up: torch.Tensor,
-                  down: torch.Tensor) -> torch.Tensor:
+                  down: torch.Tensor, tensor_memory: Optional[bool] = None) -> torch.Tensor:
     """out[t] = (1 / top) sum_k down[e] (silu(gate[e] x_t) * (up[e] x_t)), e = table[token_ids[t], k]; float32
-    [tokens, width].  gate_up [experts, 2 ff, width] (gate rows, then up rows), down [experts, width, ff]."""
+    [tokens, width].  gate_up [experts, 2 ff, width] (gate rows, then up rows), down [experts, width, ff].
+    bfloat16 steps with many pairs (``EXPERTS_TCGEN05_FROM_PAIRS``) and widths that are whole 16-byte pieces run the
+    two products on tcgen05 (``tensor_memory`` asks for or forbids it); the others on the tiled kernels."""
     _cuda(x, token_ids, table, gate_up, down)
     _contig(x, token_ids, table, gate_up, down)
     _i32(token_ids, table)
@@ -1688,6 +1694,16 @@ def table_experts(x: torch.Tensor, token_ids: torch.Tensor, table: torch.Tensor,
     h = torch.empty((pairs, ff), dtype=x.dtype, device=x.device)
     y = torch.empty((pairs, width), dtype=torch.float32, device=x.device)
     out = torch.empty((tokens, width), dtype=torch.float32, device=x.device)
+    fits = x.dtype == torch.bfloat16 and width % 8 == 0 and ff % 8 == 0 and pairs >= 128
+    if tensor_memory and not fits:
+        raise KernelError("the tcgen05 experts take bfloat16 with width and ff multiples of 8")
+    if fits and (tensor_memory if tensor_memory is not None else pairs >= EXPERTS_TCGEN05_FROM_PAIRS):
+        xs = torch.empty((pairs, width), dtype=x.dtype, device=x.device)
+        rc = load_cuda_library("experts_tcgen05.cu").b200_table_experts_tcgen05(
+            _p(x), _p(token_ids), _p(table), vocab, top, experts, _p(gate_up), _p(down), tokens, width, ff, _p(xs),
+            _p(h), _p(y), _p(route), _p(out), _p(error_word(x.device)), _stream())
+        _ok(rc, "table_experts_tcgen05", 5)
+        return out
     rc = lib.b200_table_experts(_p(x), _code(x), _p(token_ids), _p(table), vocab, top, experts, _p(gate_up), _p(down),
                                 tokens, width, ff, _p(h), _p(y), _p(route), _p(out), _p(error_word(x.device)), _stream())
     _ok(rc, "table_experts", 4)

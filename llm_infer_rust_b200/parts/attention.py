@@ -256,7 +256,7 @@ def _masked_attention(part, q, out, ctx, cache, num_heads, num_kv_heads, head_di
         for limit in (part.window, part.chunk):
             if limit:
                 bound = min(bound, limit)
-        plain = v_head_dim == head_dim and not part.chunk and sinks is None
+        plain = v_head_dim == head_dim
         per_split = ops.decode_ctas_per_split(q.dtype, ctx.num_decode, num_heads, num_kv_heads, head_dim, page, plain)
         splits = decode_splits(per_split, bound, ctx.sm_count)
         need = ops.decode_scratch_floats(ctx.num_decode, num_heads, max(head_dim, v_head_dim), splits)

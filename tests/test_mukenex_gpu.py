@@ -81,8 +81,9 @@ def test_streams_write_back_read_and_norm_in_one_kernel(S, width):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("tokens,width,ff,experts,top", [(1, 40, 24, 5, 2), (70, 44, 20, 4, 1), (300, 64, 48, 3, 3),
-                                                         (130, 256, 96, 16, 2)])
+                                                         (130, 256, 96, 16, 2), (700, 192, 136, 9, 2)])
 def test_experts_chosen_by_a_table(tokens, width, ff, experts, top, dtype):
+    """Few and many pairs (the second take the tcgen05 products in bfloat16), experts with many, few and no tokens."""
     from llm_infer_rust_b200.kernels import ops
     dev = torch.device("cuda")
     g = torch.Generator().manual_seed(tokens + top)
@@ -105,6 +106,13 @@ def test_experts_chosen_by_a_table(tokens, width, ff, experts, top, dtype):
     assert got.dtype == torch.float32
     tol = 2e-5 if dtype == torch.float32 else 2e-2
     torch.testing.assert_close(got.cpu().double(), want, rtol=tol, atol=tol)
+    if dtype == torch.bfloat16 and width % 8 == 0 and ff % 8 == 0 and tokens > 1:
+        for tensor_memory in (True, False):                       # both kinds of product on the same step
+            again = ops.table_experts(x.to(dev, dtype), ids.to(dev, torch.int32), w["table"].to(dev),
+                                      gate_up.to(dev, dtype).contiguous(), down.to(dev, dtype).contiguous(),
+                                      tensor_memory=tensor_memory)
+            torch.testing.assert_close(again.cpu().double(), want, rtol=tol, atol=tol)
+        ops.check_errors(dev)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -158,7 +166,7 @@ def _attend_in_portions(q, k, v, portions, dtype, window, chunk, sinks, scale, p
             ops.prefill_attention(qo, k_cache, v_cache, o, *args, i32([at]), i32([0]), 1, n, H, G, d, page, window,
                                   scale, v_head_dim=dv, precise_weights=True, chunk=chunk, sinks=sinks)
         else:
-            splits = 2 if at > 40 else 1
+            splits = 1 if at <= 40 else (2 if at <= 80 else 3)      # one CTA, a cluster of two, parts merged by a kernel
             need = ops.decode_scratch_floats(1, H, max(d, dv), splits)
             scratch = torch.empty(max(need, 1), device=dev)
             ops.decode_attention(qo, k_cache, v_cache, o, scratch, *args, i32([0]), 1, H, G, d, page, window, scale,
