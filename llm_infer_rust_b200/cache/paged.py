@@ -5,7 +5,7 @@ Host bookkeeping (which page holds what) lives in the C++ ``CacheManager``
 sizes the pools and owns the tensors.
 
 Grouping.  Every entry of the model's run list that keeps keys and values gets
-tensors of its own, K and V of shape [pages + 1, kv_heads, page_size, head_dim]
+tensors of its own, K and V of shape [pages + 1, kv_heads, page_size, head_dim] (K alone where a value is the leading columns of its key's row)
 (page 0 is the sink; the rows of one page and KV head are contiguous, so that the
 copy engine fetches them as one block).  Entries whose mixers have the same NEED form a group: all
 keys, or a window of W positions.  A group has its own page pool and every
@@ -84,7 +84,8 @@ def plan_cache(model, page_size: int, itemsize: int) -> CachePlan:
             groups.append(GroupPlan(need, page_size))
         g = by_need[need]
         groups[g].entries.append(e)
-        groups[g].bytes_per_page += page_size * kv.num_kv_heads * (kv.head_dim + (kv.v_head_dim or kv.head_dim)) * itemsize
+        value_width = 0 if kv.shared_values else (kv.v_head_dim or kv.head_dim)
+        groups[g].bytes_per_page += page_size * kv.num_kv_heads * (kv.head_dim + value_width) * itemsize
         group_of_entry[e] = g
     return CachePlan(groups, group_of_entry, state_entries, block_states)
 
@@ -155,7 +156,8 @@ class PagedCache:
                 if entry.reads is None:
                     shape = (plan.groups[g].num_pages + 1, kv.num_kv_heads, plan.groups[g].page_size, kv.head_dim)
                     cache.k = torch.zeros(shape, dtype=dtype, device=device)
-                    cache.v = torch.zeros(shape[:3] + (kv.v_head_dim or kv.head_dim,), dtype=dtype, device=device)
+                    if not kv.shared_values:
+                        cache.v = torch.zeros(shape[:3] + (kv.v_head_dim or kv.head_dim,), dtype=dtype, device=device)
                     owned[e] = cache
                 else:
                     cache.k, cache.v, cache.writes = owned[entry.reads].k, owned[entry.reads].v, False
@@ -172,7 +174,7 @@ class PagedCache:
         total = 0
         for c in self.layer_caches:
             if c.writes and c.k is not None:
-                total += 2 * c.k.numel() * c.k.element_size()
+                total += (c.k.numel() + (c.v.numel() if c.v is not None else 0)) * c.k.element_size()
             if c.state is not None:
                 total += c.state.numel() * c.state.element_size()
             for t in c.states.values():

@@ -147,13 +147,14 @@ __device__ __forceinline__ void warp_key_block(const T* ks, const T* vs, const f
 }
 
 // Copies key rows [first_key, first_key + 32) of one KV head into shared memory
-// with `nthreads` threads (thread index `tid`); rows at or beyond kv_end become zeros.
+// with `nthreads` threads (thread index `tid`); rows at or beyond kv_end become zeros.  A row's first `hd` elements are
+// copied; rows lie `stride` elements apart (values that are the leading columns of wider key rows: stride > hd).
 template <typename T>
 __device__ __forceinline__ void load_key_block(T* dst, const T* __restrict__ cache, const int* __restrict__ table,
                                                int page_size, int nkv, int kvh, int first_key, int kv_end, int hd,
-                                               int tid, int nthreads) {
+                                               int stride, int tid, int nthreads) {
   using G = RowGeom<T>;
-  if (hd % G::CHUNK == 0) {
+  if (hd % G::CHUNK == 0 && stride % G::CHUNK == 0) {
     // rows start on 16-byte boundaries: asynchronous 16-byte copies, zeros beyond the row and beyond the sequence
     const int row_chunks = hd / G::CHUNK;
     for (int c = tid; c < KB * G::CHUNKS; c += nthreads) {
@@ -164,7 +165,7 @@ __device__ __forceinline__ void load_key_block(T* dst, const T* __restrict__ cac
       if (valid) {
         const int page = table[key / page_size];       // cache[page][kv head][offset in page][hd]
         const size_t row = (static_cast<size_t>(page) * nkv + kvh) * page_size + key % page_size;
-        src = cache + row * hd + part * G::CHUNK;
+        src = cache + row * stride + part * G::CHUNK;
       }
       cp_async16(dst + r * G::STRIDE + part * G::CHUNK, src, valid);
     }
@@ -177,8 +178,8 @@ __device__ __forceinline__ void load_key_block(T* dst, const T* __restrict__ cac
       if (key < kv_end && 2 * pair < hd) {
         const int page = table[key / page_size];
         const size_t row = (static_cast<size_t>(page) * nkv + kvh) * page_size + key % page_size;
-        a = cache[row * hd + 2 * pair];
-        b = cache[row * hd + 2 * pair + 1];
+        a = cache[row * stride + 2 * pair];
+        b = cache[row * stride + 2 * pair + 1];
       }
       dst[r * G::STRIDE + 2 * pair] = a;
       dst[r * G::STRIDE + 2 * pair + 1] = b;
@@ -199,7 +200,7 @@ prefill_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
                          const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                          const int* __restrict__ prefix_len, const int* __restrict__ rows, int nh, int nkv,
                          int page_size, int window, float scale, int tile_tokens, int head_chunks, int hd,
-                         int hd_v, float softcap, int chunk, const float* __restrict__ sinks) {
+                         int hd_v, float softcap, int chunk, const float* __restrict__ sinks, int v_stride) {
   using G = RowGeom<T>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* qs = reinterpret_cast<float*>(smem_raw);                        // [32][D]
@@ -246,8 +247,8 @@ prefill_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
   st.init();
   for (int kb = k_begin; kb < kv_end; kb += KB) {
     __syncthreads();                                   // the previous block is no longer read
-    load_key_block<T>(ks, k_cache, table, page_size, nkv, kvh, kb, kv_end, hd, threadIdx.x, blockDim.x);
-    load_key_block<T>(vs, v_cache, table, page_size, nkv, kvh, kb, kv_end, hd_v, threadIdx.x, blockDim.x);
+    load_key_block<T>(ks, k_cache, table, page_size, nkv, kvh, kb, kv_end, hd, hd, threadIdx.x, blockDim.x);
+    load_key_block<T>(vs, v_cache, table, page_size, nkv, kvh, kb, kv_end, hd_v, v_stride, threadIdx.x, blockDim.x);
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
@@ -290,7 +291,7 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
                         const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_q,
                         const int* __restrict__ kv_len, const int* __restrict__ rows, int nh, int nkv,
                         int page_size, int window, float scale, int vec_groups, int stages, int hd, int hd_v,
-                        float softcap, int chunk, const float* __restrict__ sinks) {
+                        float softcap, int chunk, const float* __restrict__ sinks, int v_stride) {
   using G = RowGeom<T>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* qs = reinterpret_cast<float*>(smem_raw);                        // [NV][D]
@@ -333,8 +334,8 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
   for (int s = 0; s < stages - 1; ++s) {
     if (issue < blk_hi) {
       T* t = my_tiles + s * tile_elems;
-      load_key_block<T>(t, k_cache, table, page_size, nkv, kvh, k_begin + issue * KB, kv_end, hd, lane, 32);
-      load_key_block<T>(t + KB * G::STRIDE, v_cache, table, page_size, nkv, kvh, k_begin + issue * KB, kv_end, hd_v, lane, 32);
+      load_key_block<T>(t, k_cache, table, page_size, nkv, kvh, k_begin + issue * KB, kv_end, hd, hd, lane, 32);
+      load_key_block<T>(t + KB * G::STRIDE, v_cache, table, page_size, nkv, kvh, k_begin + issue * KB, kv_end, hd_v, v_stride, lane, 32);
     }
     cp_async_commit();
     issue += DEC_WARPS;
@@ -345,16 +346,16 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
       const int s_issue = (stage + stages - 1) % stages;
       if (issue < blk_hi) {
         T* t = my_tiles + s_issue * tile_elems;
-        load_key_block<T>(t, k_cache, table, page_size, nkv, kvh, k_begin + issue * KB, kv_end, hd, lane, 32);
-        load_key_block<T>(t + KB * G::STRIDE, v_cache, table, page_size, nkv, kvh, k_begin + issue * KB, kv_end, hd_v, lane, 32);
+        load_key_block<T>(t, k_cache, table, page_size, nkv, kvh, k_begin + issue * KB, kv_end, hd, hd, lane, 32);
+        load_key_block<T>(t + KB * G::STRIDE, v_cache, table, page_size, nkv, kvh, k_begin + issue * KB, kv_end, hd_v, v_stride, lane, 32);
       }
       cp_async_commit();
       issue += DEC_WARPS;
       cp_async_wait<1>();          // stages is 1 or 2: all but the newest group have landed
     } else {
       T* t = my_tiles;
-      load_key_block<T>(t, k_cache, table, page_size, nkv, kvh, k_begin + blk * KB, kv_end, hd, lane, 32);
-      load_key_block<T>(t + KB * G::STRIDE, v_cache, table, page_size, nkv, kvh, k_begin + blk * KB, kv_end, hd_v, lane, 32);
+      load_key_block<T>(t, k_cache, table, page_size, nkv, kvh, k_begin + blk * KB, kv_end, hd, hd, lane, 32);
+      load_key_block<T>(t + KB * G::STRIDE, v_cache, table, page_size, nkv, kvh, k_begin + blk * KB, kv_end, hd_v, v_stride, lane, 32);
       cp_async_commit();
       cp_async_wait<0>();
     }
@@ -438,7 +439,7 @@ static int launch_prefill(const void* q, const void* kc, const void* vc, void* o
                           int table_stride, const int* cu_q, const int* kv_len, const int* prefix_len,
                           const int* rows, int n_rows, int max_q_len, int nh, int nkv, int page_size, int window,
                           float scale, int hd, int hd_v, float softcap, int chunk, const float* sinks,
-                          cudaStream_t stream) {
+                          int v_stride, cudaStream_t stream) {
   using G = RowGeom<T>;
   const int group = nh / nkv;
   const int head_chunks = (group + 31) / 32;                  // more than 32 query heads per KV head: several CTAs
@@ -456,7 +457,7 @@ static int launch_prefill(const void* q, const void* kc, const void* vc, void* o
   prefill_attention_kernel<T><<<grid, PF_WARPS * 32, smem, stream>>>(
       static_cast<const T*>(q), static_cast<const T*>(kc), static_cast<const T*>(vc), static_cast<T*>(out),
       block_table, table_stride, cu_q, kv_len, prefix_len, rows, nh, nkv, page_size, window, scale, tile_tokens,
-      head_chunks, hd, hd_v, softcap, chunk, sinks);
+      head_chunks, hd, hd_v, softcap, chunk, sinks, v_stride > 0 ? v_stride : hd_v);
   return b200_check_launch();
 }
 
@@ -465,7 +466,7 @@ static int launch_decode(const void* q, const void* kc, const void* vc, void* ou
                          const int* block_table, int table_stride, const int* cu_q, const int* kv_len,
                          const int* rows, int n_rows, int nh, int nkv, int page_size, int window, float scale,
                          int splits, int hd, int hd_v, float softcap, int chunk, const float* sinks,
-                         cudaStream_t stream) {
+                         int v_stride, cudaStream_t stream) {
   using G = RowGeom<T>;
   const int group = nh / nkv;
   const int vec_groups = (group + NV - 1) / NV;
@@ -491,7 +492,7 @@ static int launch_decode(const void* q, const void* kc, const void* vc, void* ou
   decode_attention_kernel<T, DEC_WARPS><<<grid, DEC_WARPS * 32, smem, stream>>>(
       static_cast<const T*>(q), static_cast<const T*>(kc), static_cast<const T*>(vc), static_cast<T*>(out),
       part_acc, part_ml, block_table, table_stride, cu_q, kv_len, rows, nh, nkv, page_size, window, scale,
-      vec_groups, stages, hd, hd_v, softcap, chunk, sinks);
+      vec_groups, stages, hd, hd_v, softcap, chunk, sinks, v_stride > 0 ? v_stride : hd_v);
   int rc = b200_check_launch();
   if (rc != 0 || splits == 1) return rc;
   dim3 mgrid(n_rows, nh);
@@ -508,7 +509,7 @@ B200_EXPORT int b200_prefill_attention(const void* q, const void* k_cache, const
                                        const int* kv_len, const int* prefix_len, const int* rows, int n_rows,
                                        int max_q_len, int nh, int nkv, int page_size, int window, float scale,
                                        int dtype, int head_dim, int v_head_dim, float softcap, int chunk,
-                                       const float* sinks, cudaStream_t stream) {
+                                       const float* sinks, int v_stride, cudaStream_t stream) {
   if (n_rows <= 0 || max_q_len <= 0) return 0;
   if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0) return B200_BAD_SIZE;
   if (head_dim <= 0 || head_dim > D || (head_dim & 1)) return B200_BAD_SIZE;
@@ -516,11 +517,11 @@ B200_EXPORT int b200_prefill_attention(const void* q, const void* k_cache, const
   if (dtype == B200_F32)
     return launch_prefill<float>(q, k_cache, v_cache, out, block_table, table_stride, cu_q, kv_len, prefix_len,
                                  rows, n_rows, max_q_len, nh, nkv, page_size, window, scale, head_dim, v_head_dim,
-                                 softcap, chunk, sinks, stream);
+                                 softcap, chunk, sinks, v_stride, stream);
   if (dtype == B200_BF16)
     return launch_prefill<__nv_bfloat16>(q, k_cache, v_cache, out, block_table, table_stride, cu_q, kv_len,
                                          prefix_len, rows, n_rows, max_q_len, nh, nkv, page_size, window, scale,
-                                         head_dim, v_head_dim, softcap, chunk, sinks, stream);
+                                         head_dim, v_head_dim, softcap, chunk, sinks, v_stride, stream);
   return B200_BAD_DTYPE;
 }
 
@@ -536,7 +537,7 @@ B200_EXPORT int b200_decode_attention(const void* q, const void* k_cache, const 
                                       const int* cu_q, const int* kv_len, const int* rows, int n_rows, int nh,
                                       int nkv, int page_size, int window, float scale, int splits, int dtype,
                                       int head_dim, int v_head_dim, float softcap, int chunk, const float* sinks,
-                                      cudaStream_t stream) {
+                                      int v_stride, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || splits <= 0) return B200_BAD_SIZE;
   if (head_dim <= 0 || head_dim > D || (head_dim & 1)) return B200_BAD_SIZE;
@@ -546,10 +547,10 @@ B200_EXPORT int b200_decode_attention(const void* q, const void* k_cache, const 
   if (dtype == B200_F32)
     return launch_decode<float>(q, k_cache, v_cache, out, part_acc, part_ml, block_table, table_stride, cu_q,
                                 kv_len, rows, n_rows, nh, nkv, page_size, window, scale, splits, head_dim, v_head_dim,
-                                softcap, chunk, sinks, stream);
+                                softcap, chunk, sinks, v_stride, stream);
   if (dtype == B200_BF16)
     return launch_decode<__nv_bfloat16>(q, k_cache, v_cache, out, part_acc, part_ml, block_table, table_stride,
                                         cu_q, kv_len, rows, n_rows, nh, nkv, page_size, window, scale, splits,
-                                        head_dim, v_head_dim, softcap, chunk, sinks, stream);
+                                        head_dim, v_head_dim, softcap, chunk, sinks, v_stride, stream);
   return B200_BAD_DTYPE;
 }

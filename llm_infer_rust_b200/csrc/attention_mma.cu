@@ -36,16 +36,33 @@
 #ifndef HEAD_DIM
 #error "compile with -DHEAD_DIM=<head size, a multiple of 16>"
 #endif
-static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 256, "the tensor-core kernels take head sizes 16..256 in steps of 16");
+// A second form serves attention over a latent (compile with -DV_SHARED=1 -DV_DIM=<columns>): a token has ONE key row
+// of HEAD_DIM columns (up to 512) that every query head reads, and its value is a range of V_DIM columns of that same
+// row (from column ScoreForm::v_col0 on), so a block's tile is fetched once and serves both products.  The output
+// goes to columns out_col0 .. out_col0 + V_DIM of rows out_width wide: values wider than 256 columns take several
+// launches, each with the scores computed again.
+#ifndef V_SHARED
+#define V_SHARED 0
+#endif
+#ifndef V_DIM
+#define V_DIM HEAD_DIM
+#endif
+static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= (V_SHARED ? 512 : 256),
+              "the tensor-core kernels take head sizes 16..256 in steps of 16 (keys of a shared row: up to 512)");
+static_assert(V_DIM % 16 == 0 && V_DIM >= 16 && V_DIM <= 256 && V_DIM <= HEAD_DIM && (V_SHARED || V_DIM == HEAD_DIM),
+              "values are as wide as keys, or 16..256 columns of the keys' own rows");
 
 typedef __nv_bfloat16 bf16;
 namespace cg = cooperative_groups;
 constexpr int D = HEAD_DIM;
+constexpr int DV = V_DIM;          // columns of a value and of an output tile
+constexpr bool kShared = V_SHARED != 0;
 constexpr int LD = D + 8;          // padded row of the query tile (16 bytes of padding): conflict-free ldmatrix
 constexpr int KB = 32;             // keys per block
 constexpr int NB = (D + 63) / 64;  // 64-dim (128-byte) column boxes per row
 constexpr int HALF_BYTES = KB * 128;              // one column box of a block: 32 rows x 128 bytes
-constexpr int TILE_BYTES = 2 * NB * HALF_BYTES;   // keys then values of one block
+constexpr int TILE_BYTES = (kShared ? 1 : 2) * NB * HALF_BYTES;   // keys then values of one block (one tile for both)
+constexpr int V_OFFSET = kShared ? 0 : NB * HALF_BYTES;           // where a block's values begin in its tile
 constexpr int QROWS = 16;          // rows of the A operand: query heads of one KV head
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
@@ -79,6 +96,8 @@ struct ScoreForm {
   int split_p;
   int chunk;
   const float* sinks;
+  int v_col0;                  // shared rows: first column of the values
+  int out_width, out_col0;     // an output row's width and the first column that this launch writes
 };
 // The sum of a row's weights with the sink's term (the row's maximum m is in log2 units).
 __device__ __forceinline__ float with_sink(const ScoreForm& sf, int head, float m, float l) {
@@ -127,15 +146,16 @@ __device__ __forceinline__ void fetch_block(unsigned char* tile, const CUtensorM
                                             int kv_end, uint64_t* bar, int lane) {
   const int n_sub = (min(KB, kv_end - first_key) + box_rows - 1) / box_rows;
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // earlier reads and writes of the tile come first
-  if (lane == 0) mbar_expect_tx(bar, static_cast<uint32_t>(n_sub) * 2u * NB * box_rows * 128u);
+  if (lane == 0) mbar_expect_tx(bar, static_cast<uint32_t>(n_sub) * (kShared ? 1u : 2u) * NB * box_rows * 128u);
   __syncwarp();
   if (lane < n_sub) {
     const int key0 = first_key + lane * box_rows;
-    const int y = (page * nkv + kvh) * page_size + key0 % page_size;
+    const int y = kShared ? page * page_size + key0 % page_size          // one row a token for every head
+                          : (page * nkv + kvh) * page_size + key0 % page_size;
 #pragma unroll
     for (int h = 0; h < NB; ++h) {
       tma_load_2d(tile + h * HALF_BYTES + lane * box_rows * 128, kmap, h * 64, y, bar);
-      tma_load_2d(tile + (NB + h) * HALF_BYTES + lane * box_rows * 128, vmap, h * 64, y, bar);
+      if constexpr (!kShared) tma_load_2d(tile + (NB + h) * HALF_BYTES + lane * box_rows * 128, vmap, h * 64, y, bar);
     }
   }
 }
@@ -150,11 +170,11 @@ __device__ __forceinline__ int lane_page(const int* __restrict__ table, int page
 
 // State of one warp: 16 query rows x D outputs in mma accumulator layout.
 struct WarpAcc {
-  float o[D / 8][4];
+  float o[DV / 8][4];
   float m[2], l[2];          // rows lane/4 and lane/4 + 8; l is this thread's part of the row sum
   __device__ __forceinline__ void init() {
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+    for (int i = 0; i < DV / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
     m[0] = m[1] = -INFINITY; l[0] = l[1] = 0.0f;
   }
 };
@@ -232,7 +252,7 @@ __device__ __forceinline__ void block_mma(const bf16* qs, const unsigned char* k
   st.l[1] = st.l[1] * c1 + sum1;
   if (__any_sync(0xffffffffu, c0 != 1.0f || c1 != 1.0f)) {       // no row's maximum moved: nothing to rescale
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i) { st.o[i][0] *= c0; st.o[i][1] *= c0; st.o[i][2] *= c1; st.o[i][3] *= c1; }
+    for (int i = 0; i < DV / 8; ++i) { st.o[i][0] *= c0; st.o[i][1] *= c0; st.o[i][2] *= c1; st.o[i][3] *= c1; }
   }
 #pragma unroll
   for (int kk = 0; kk < 2; ++kk) {
@@ -248,10 +268,11 @@ __device__ __forceinline__ void block_mma(const bf16* qs, const unsigned char* k
       a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
       a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
     }
+    const int v_chunk0 = kShared ? sf.v_col0 >> 3 : 0;
 #pragma unroll
-    for (int dn = 0; dn < D / 8; dn += 2) {
+    for (int dn = 0; dn < DV / 8; dn += 2) {
       uint32_t b[4];
-      ldmatrix_x4_trans(b, vs + swz(kk * 16 + (mi & 1) * 8 + r8, dn + (mi >> 1)));
+      ldmatrix_x4_trans(b, vs + swz(kk * 16 + (mi & 1) * 8 + r8, v_chunk0 + dn + (mi >> 1)));
       mma_bf16(st.o[dn], a, b[0], b[1]);
       mma_bf16(st.o[dn + 1], a, b[2], b[3]);
       if (SHAPED && sf.split_p) {
@@ -357,14 +378,14 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
       // Value rows beyond the sequence: whatever the page holds there must not reach P.V.
       const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-      for (int c = 0; c < NB * 8; ++c) *reinterpret_cast<uint4*>(t + NB * HALF_BYTES + (c >> 3) * HALF_BYTES + lane * 128 + (c & 7) * 16) = zero;
+      for (int c = 0; c < NB * 8; ++c) *reinterpret_cast<uint4*>(t + V_OFFSET + (c >> 3) * HALF_BYTES + lane * 128 + (c & 7) * 16) = zero;
     }
     __syncwarp();
     if (first_key + KB <= kv_end && (window <= 0 || first_key > qp - window) &&
         (sf.chunk <= 0 || first_key >= qp - qp % sf.chunk))
-      block_mma<false, SHAPED>(qs, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos0, qpos1, sf, st);
+      block_mma<false, SHAPED>(qs, t, t + V_OFFSET, first_key, kv_end, window, qpos0, qpos1, sf, st);
     else
-      block_mma<true, SHAPED>(qs, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos0, qpos1, sf, st);
+      block_mma<true, SHAPED>(qs, t, t + V_OFFSET, first_key, kv_end, window, qpos0, qpos1, sf, st);
     __syncwarp();                                      // every lane is done reading before the stage is refilled
     if (++stage == STAGES) { stage = 0; parity ^= 1u; }
   }
@@ -373,7 +394,8 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
   __syncthreads();
   // Merge the warps through shared memory: [WARPS][group][D + 2] floats over the tile area.
   float* merge = reinterpret_cast<float*>(tiles);     // all copies have landed and been used
-  constexpr int MS = D + 2;
+  constexpr int MS = DV + 2;
+  const int ow = kShared ? sf.out_width : D, oc = kShared ? sf.out_col0 : 0;     // an output row and this launch's columns
   float* mine = merge + WARPS * QROWS * MS;           // [group][MS]: the CTA's own combined part
   const int t2 = (lane & 3) * 2;
 #pragma unroll
@@ -382,39 +404,39 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     if (r < group) {
       float* dst = merge + (warp * group + r) * MS;
 #pragma unroll
-      for (int dn = 0; dn < D / 8; ++dn) {
+      for (int dn = 0; dn < DV / 8; ++dn) {
         dst[dn * 8 + t2] = st.o[dn][2 * half];
         dst[dn * 8 + t2 + 1] = st.o[dn][2 * half + 1];
       }
-      if ((lane & 3) == 0) { dst[D] = st.m[half]; dst[D + 1] = st.l[half]; }
+      if ((lane & 3) == 0) { dst[DV] = st.m[half]; dst[DV + 1] = st.l[half]; }
     }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < group * D; i += blockDim.x) {
-    const int r = i / D, dim = i - r * D;
+  for (int i = threadIdx.x; i < group * DV; i += blockDim.x) {
+    const int r = i / DV, dim = i - r * DV;
     float m = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < WARPS; ++w) m = fmaxf(m, merge[(w * group + r) * MS + D]);
+    for (int w = 0; w < WARPS; ++w) m = fmaxf(m, merge[(w * group + r) * MS + DV]);
     float l = 0.0f, o = 0.0f;
     if (m != -INFINITY) {
 #pragma unroll
       for (int w = 0; w < WARPS; ++w) {
         const float* src = merge + (w * group + r) * MS;
-        const float f = exp2f(src[D] - m);
-        l += src[D + 1] * f;
+        const float f = exp2f(src[DV] - m);
+        l += src[DV + 1] * f;
         o += src[dim] * f;
       }
     }
     const int head = head0 + r;
     if (splits == 1) {
       l = with_sink(sf, head, m, l);
-      out[(static_cast<size_t>(tok) * nh + head) * D + dim] = __float2bfloat16_rn(l > 0.0f ? o / l : 0.0f);
+      out[(static_cast<size_t>(tok) * nh + head) * ow + oc + dim] = __float2bfloat16_rn(l > 0.0f ? o / l : 0.0f);
     } else if (cluster_merge) {
       mine[r * MS + dim] = o;                          // this CTA's part, for the cluster's first CTA to read
-      if (dim == 0) { mine[r * MS + D] = m; mine[r * MS + D + 1] = l; }
+      if (dim == 0) { mine[r * MS + DV] = m; mine[r * MS + DV + 1] = l; }
     } else {
       const size_t slot = (static_cast<size_t>(blockIdx.z) * nh + head) * splits + split;
-      part_acc[slot * D + dim] = o;
+      part_acc[slot * DV + dim] = o;
       if (dim == 0) { part_ml[slot * 2] = m; part_ml[slot * 2 + 1] = l; }
     }
   }
@@ -424,21 +446,21 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
   cg::cluster_group cluster = cg::this_cluster();
   cluster.sync();
   if (split == 0) {
-    for (int i = threadIdx.x; i < group * D; i += blockDim.x) {
-      const int r = i / D, dim = i - r * D;
+    for (int i = threadIdx.x; i < group * DV; i += blockDim.x) {
+      const int r = i / DV, dim = i - r * DV;
       float m = -INFINITY;
-      for (int s = 0; s < splits; ++s) m = fmaxf(m, cluster.map_shared_rank(mine, s)[r * MS + D]);
+      for (int s = 0; s < splits; ++s) m = fmaxf(m, cluster.map_shared_rank(mine, s)[r * MS + DV]);
       float l = 0.0f, o = 0.0f;
       if (m != -INFINITY) {
         for (int s = 0; s < splits; ++s) {
           const float* src = cluster.map_shared_rank(mine, s) + r * MS;
-          const float f = exp2f(src[D] - m);
-          l += src[D + 1] * f;
+          const float f = exp2f(src[DV] - m);
+          l += src[DV + 1] * f;
           o += src[dim] * f;
         }
         l = with_sink(sf, head0 + r, m, l);
       }
-      out[(static_cast<size_t>(tok) * nh + head0 + r) * D + dim] = __float2bfloat16_rn(l > 0.0f ? o / l : 0.0f);
+      out[(static_cast<size_t>(tok) * nh + head0 + r) * ow + oc + dim] = __float2bfloat16_rn(l > 0.0f ? o / l : 0.0f);
     }
   }
   cluster.sync();                                      // nobody leaves while its shared memory may still be read
@@ -448,7 +470,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
 __global__ void decode_mma_merge_kernel(bf16* __restrict__ out, const float* __restrict__ part_acc,
                                         const float* __restrict__ part_ml, const int* __restrict__ cu_q,
                                         const int* __restrict__ rows, int nh, int splits,
-                                        const float* __restrict__ sinks) {
+                                        const float* __restrict__ sinks, int out_width, int out_col0) {
   pdl_launch_dependents();
   pdl_wait();
   const int head = blockIdx.y;
@@ -456,17 +478,17 @@ __global__ void decode_mma_merge_kernel(bf16* __restrict__ out, const float* __r
   const size_t base = (static_cast<size_t>(blockIdx.x) * nh + head) * splits;
   float m = -INFINITY;
   for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
-  for (int dim = threadIdx.x; dim < D; dim += blockDim.x) {
+  for (int dim = threadIdx.x; dim < DV; dim += blockDim.x) {
     float l = 0.0f, o = 0.0f;
     if (m != -INFINITY) {
       for (int s = 0; s < splits; ++s) {
         const float f = exp2f(part_ml[(base + s) * 2] - m);
         l += part_ml[(base + s) * 2 + 1] * f;
-        o += part_acc[(base + s) * D + dim] * f;
+        o += part_acc[(base + s) * DV + dim] * f;
       }
       if (sinks != nullptr && l > 0.0f) l += exp2f(sinks[head] * 1.4426950408889634f - m);
     }
-    out[(static_cast<size_t>(tok) * nh + head) * D + dim] = __float2bfloat16_rn(l > 0.0f ? o / l : 0.0f);
+    out[(static_cast<size_t>(tok) * nh + head) * out_width + out_col0 + dim] = __float2bfloat16_rn(l > 0.0f ? o / l : 0.0f);
   }
 }
 
@@ -590,7 +612,7 @@ prefill_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
       // masked for every query of the tile): keep them out of P.V.
       const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-      for (int c = 0; c < NB * 8; ++c) *reinterpret_cast<uint4*>(t + NB * HALF_BYTES + (c >> 3) * HALF_BYTES + lane * 128 + (c & 7) * 16) = zero;
+      for (int c = 0; c < NB * 8; ++c) *reinterpret_cast<uint4*>(t + V_OFFSET + (c >> 3) * HALF_BYTES + lane * 128 + (c & 7) * 16) = zero;
     }
     __syncwarp();
     if (w_tok_hi >= w_tok_lo && first_key <= w_p_hi && first_key + KB > w_first_key) {
@@ -599,9 +621,9 @@ prefill_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
                                (window <= 0 || first_key > w_p_hi - window) &&
                                (sf.chunk <= 0 || first_key >= w_p_hi - w_p_hi % sf.chunk);
       if (all_visible)
-        block_mma<false, SHAPED>(my_q, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos[0], qpos[1], sf, st);
+        block_mma<false, SHAPED>(my_q, t, t + V_OFFSET, first_key, kv_end, window, qpos[0], qpos[1], sf, st);
       else
-        block_mma<true, SHAPED>(my_q, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos[0], qpos[1], sf, st);
+        block_mma<true, SHAPED>(my_q, t, t + V_OFFSET, first_key, kv_end, window, qpos[0], qpos[1], sf, st);
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(empty + s);
@@ -618,11 +640,12 @@ prefill_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
   for (int h = 0; h < 2; ++h) {
     if (tok_of[h] < 0) continue;
     const int head = head0 + (g + 8 * h) % group;
-    bf16* dst = out + (static_cast<size_t>(q_begin + tok0 + tok_of[h]) * nh + head) * D;
+    bf16* dst = out + (static_cast<size_t>(q_begin + tok0 + tok_of[h]) * nh + head) * (kShared ? sf.out_width : D) +
+                (kShared ? sf.out_col0 : 0);
     const float l = with_sink(sf, head, st.m[h], st.l[h]);
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
 #pragma unroll
-    for (int dn = 0; dn < D / 8; ++dn)
+    for (int dn = 0; dn < DV / 8; ++dn)
       *reinterpret_cast<uint32_t*>(dst + dn * 8 + t2) = pack_bf16(st.o[dn][2 * h] * inv, st.o[dn][2 * h + 1] * inv);
   }
 }
@@ -637,7 +660,7 @@ constexpr int kWarps = kFixedBytes + 6 * 2 * TILE_BYTES <= kSmemLimit ? 6 : (kFi
 constexpr int kStages = kFixedBytes + kWarps * 3 * TILE_BYTES <= kSmemLimit ? 3 : 2;
 static_assert(kFixedBytes + kWarps * kStages * TILE_BYTES <= kSmemLimit, "the key blocks must fit shared memory");
 static_assert(kWarps * kStages * sizeof(uint64_t) <= kBarBytes, "barriers");
-static_assert(static_cast<size_t>(kWarps + 1) * QROWS * (D + 2) * sizeof(float) <= static_cast<size_t>(kWarps) * kStages * TILE_BYTES,
+static_assert(static_cast<size_t>(kWarps + 1) * QROWS * (DV + 2) * sizeof(float) <= static_cast<size_t>(kWarps) * kStages * TILE_BYTES,
               "the merge area lies over the tiles");
 
 B200_EXPORT int b200_attention_mma_head_dim() { return D; }
@@ -675,7 +698,8 @@ B200_EXPORT int b200_kv_tensor_map(void* out_map, const void* cache, long long r
   return 0;
 }
 
-static ScoreForm score_form(float scale, float softcap, int split_p, int chunk, const float* sinks) {
+static ScoreForm score_form(float scale, float softcap, int split_p, int chunk, const float* sinks, int v_col0 = 0,
+                            int out_width = D, int out_col0 = 0) {
   ScoreForm sf;
   sf.scale_log2 = scale * 1.4426950408889634f;
   sf.tanh_in = softcap > 0.0f ? scale / softcap : 0.0f;
@@ -683,6 +707,9 @@ static ScoreForm score_form(float scale, float softcap, int split_p, int chunk, 
   sf.split_p = split_p;
   sf.chunk = chunk;
   sf.sinks = sinks;
+  sf.v_col0 = v_col0;
+  sf.out_width = out_width;
+  sf.out_col0 = out_col0;
   return sf;
 }
 
@@ -693,8 +720,8 @@ B200_EXPORT int b200_decode_attention_mma(const void* q, const void* k_map, cons
                                           float* scratch, const int* block_table, int table_stride,
                                           const int* cu_q, const int* kv_len, const int* rows, int n_rows, int nh,
                                           int nkv, int page_size, int window, float scale, int splits,
-                                          float softcap, int split_p, int chunk, const float* sinks, int* err,
-                                          cudaStream_t stream) {
+                                          float softcap, int split_p, int chunk, const float* sinks, int v_col0,
+                                          int out_width, int out_col0, int* err, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || nh / nkv > QROWS || page_size <= 0 || splits <= 0) return B200_BAD_SIZE;
   if ((page_size & (page_size - 1)) != 0) return B200_BAD_SIZE;
@@ -712,7 +739,7 @@ B200_EXPORT int b200_decode_attention_mma(const void* q, const void* k_map, cons
   memcpy(&kmap, k_map, sizeof(kmap));
   memcpy(&vmap, v_map, sizeof(vmap));
   float* part_acc = scratch;
-  float* part_ml = scratch + static_cast<size_t>(n_rows) * nh * splits * D;
+  float* part_ml = scratch + static_cast<size_t>(n_rows) * nh * splits * DV;
   dim3 grid(splits, nkv, n_rows);
   // Two, four or eight splits are the CTAs of one cluster and combine their parts through distributed shared memory;
   // other counts leave them in `scratch` for a kernel of its own.
@@ -731,11 +758,12 @@ B200_EXPORT int b200_decode_attention_mma(const void* q, const void* k_map, cons
   int rc = b200_launch(kernel, grid, dim3(kWarps * 32), smem, stream, cluster_merge ? splits : 0,
                        kmap, vmap, static_cast<const bf16*>(q), static_cast<bf16*>(out), part_acc, part_ml, block_table,
                        table_stride, cu_q, kv_len, rows, nh, nkv, page_size, box_rows, window,
-                       score_form(scale, softcap, split_p, chunk, sinks), cluster_merge ? 1 : 0, err);
+                       score_form(scale, softcap, split_p, chunk, sinks, v_col0, kShared ? out_width : D, kShared ? out_col0 : 0), cluster_merge ? 1 : 0, err);
   if (rc != 0 || splits == 1 || cluster_merge) return rc;
   dim3 mgrid(n_rows, nh);
   return b200_launch(decode_mma_merge_kernel, mgrid, dim3(D >= 128 ? 128 : 64), 0, stream, 0, static_cast<bf16*>(out),
-                     static_cast<const float*>(part_acc), static_cast<const float*>(part_ml), cu_q, rows, nh, splits, sinks);
+                     static_cast<const float*>(part_acc), static_cast<const float*>(part_ml), cu_q, rows, nh, splits, sinks,
+                     kShared ? out_width : D, kShared ? out_col0 : 0);
 }
 
 constexpr size_t kPfQBytes = PF_ROWS * LD * sizeof(bf16);
@@ -749,8 +777,8 @@ B200_EXPORT int b200_prefill_attention_mma(const void* q, const void* k_map, con
                                            const int* block_table, int table_stride, const int* cu_q,
                                            const int* kv_len, const int* prefix_len, const int* rows, int n_rows,
                                            int max_q_len, int nh, int nkv, int page_size, int window, float scale,
-                                           float softcap, int split_p, int chunk, const float* sinks, int* err,
-                                          cudaStream_t stream) {
+                                           float softcap, int split_p, int chunk, const float* sinks, int v_col0,
+                                          int out_width, int out_col0, int* err, cudaStream_t stream) {
   if (n_rows <= 0 || max_q_len <= 0) return 0;
   if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || nh / nkv > QROWS || page_size <= 0) return B200_BAD_SIZE;
   if ((page_size & (page_size - 1)) != 0) return B200_BAD_SIZE;
@@ -773,6 +801,6 @@ B200_EXPORT int b200_prefill_attention_mma(const void* q, const void* k_map, con
   dim3 grid(nkv, n_rows, n_tiles);
   kernel<<<grid, PF_WARPS * 32, smem, stream>>>(
       kmap, vmap, static_cast<const bf16*>(q), static_cast<bf16*>(out), block_table, table_stride, cu_q, kv_len,
-      prefix_len, rows, nh, nkv, page_size, box_rows, window, score_form(scale, softcap, split_p, chunk, sinks), err);
+      prefix_len, rows, nh, nkv, page_size, box_rows, window, score_form(scale, softcap, split_p, chunk, sinks, v_col0, kShared ? out_width : D, kShared ? out_col0 : 0), err);
   return b200_check_launch();
 }

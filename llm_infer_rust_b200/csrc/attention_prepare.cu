@@ -10,7 +10,8 @@
 // (2) latent_prepare: attention over a narrow latent.  The packed row holds per head [d plain | r rotated] query
 //     coordinates (nh * (d + r)), then the down projection [c_dim latent | r rotated key part].  The latent is
 //     RMS-normed (weight w_c) and, with the rotated key part behind it, is the ONE key of the token
-//     (c_dim + r wide, shared by all heads); the latent alone is its value.  The query against that key is
+//     (c_dim + r wide, shared by all heads); the latent alone is its value (stored a second time only if a value cache
+//     is given: attention can read it out of the key rows).  The query against that key is
 //     [q_lat (c_dim) | rotated (r)], where q_lat[h] = W_uk[h]^T q_plain[h] was multiplied before
 //     (q_lat: [nh, tokens, c_dim]), since q_plain . (W_uk[h] c) = (W_uk[h]^T q_plain) . c.
 //
@@ -150,9 +151,11 @@ latent_prepare_kernel(const T* __restrict__ x, int in_stride, const T* __restric
   const int slot = slots[t];
   T* kd = cache_row(k_cache, slot, 0, 1, page_size, cache_slots, c_dim + r, lane, err);
   if (kd == nullptr) return;
-  T* vd = cache_row(v_cache, slot, 0, 1, page_size, cache_slots, c_dim, lane, err);
   for (int i = lane; i < c_dim + r; i += 32) kd[i] = from_f32<T>(row[i]);
-  for (int i = lane; i < c_dim; i += 32) vd[i] = from_f32<T>(row[i]);
+  if (v_cache != nullptr) {                          // a cache that keeps the values apart (else they are read from the key rows)
+    T* vd = cache_row(v_cache, slot, 0, 1, page_size, cache_slots, c_dim, lane, err);
+    for (int i = lane; i < c_dim; i += 32) vd[i] = from_f32<T>(row[i]);
+  }
 }
 
 B200_EXPORT int b200_heads_prepare(const void* x, int dtype, int in_stride, const float* bias, const float* q_w,

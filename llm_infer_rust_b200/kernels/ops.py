@@ -292,7 +292,7 @@ def prefill_attention(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefi
                       max_q_len, num_heads, num_kv_heads, head_dim, page_size, window, scale,
                       tiles_per_cta: int = 0, v_head_dim: Optional[int] = None, softcap: float = 0.0,
                       precise_weights: bool = False, chunk: Optional[int] = None,
-                      sinks: Optional[torch.Tensor] = None) -> None:
+                      sinks: Optional[torch.Tensor] = None, shared_values: bool = False) -> None:
     """Causal attention of prompt portions over the paged cache (rows: which batch rows).
 
     ``v_head_dim``: the width of a value (and of an output) vector where it differs from a key's;
@@ -303,7 +303,9 @@ def prefill_attention(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefi
 
     ``chunk`` C: a query at position p sees only keys from p - p % C on (its own block of C positions, counted from
     the sequence's start); ``sinks`` (float32, one per query head): exp(sink) joins the softmax's denominator.  Both
-    are served by the mma.sync and the all-sizes kernels, not by the tcgen05 one.
+    are served by the mma.sync and the all-sizes kernels, not by the tcgen05 one.  ``shared_values``: one KV head
+    whose values are the first ``v_head_dim`` columns of the key rows (``v_cache`` is not read and may be None): the
+    mma.sync kernels fetch a block's rows once for both products and take the values in column tiles.
 
     ``tiles_per_cta`` (head size 128 on the tcgen05 kernel only): 1 or 2 tiles of 128 query vectors per
     CTA, 0 lets the kernel's launcher choose by the size of the grid."""
@@ -317,7 +319,23 @@ def prefill_attention(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefi
     cap = float(softcap or 0.0)
     _check_sinks(sinks, num_heads)
     plain_mask = not chunk and sinks is None
-    if dv == head_dim and decode_uses_tensor_cores(q.dtype, num_heads, num_kv_heads, head_dim, page_size):
+    if shared_values:
+        if num_kv_heads != 1 or k_cache.shape[1] != 1:
+            raise KernelError("values that are columns of the key rows need one KV head")
+        if latent_uses_tensor_cores(q.dtype, num_heads, head_dim, dv, page_size):
+            tile, group = shared_value_tile(dv), latent_head_group(num_heads)
+            lib = _attention_mma(head_dim, tile)
+            kmap = kv_tensor_map(k_cache, min(page_size, 32), lib)
+            for col0 in range(0, dv, tile):
+                rc = lib.b200_prefill_attention_mma(
+                    _p(q), kmap, kmap, _p(out), _p(block_table), block_table.shape[-1], _p(cu_q), _p(kv_len),
+                    _p(prefix_len), _p(rows), n_rows, max_q_len, num_heads, num_heads // group, page_size,
+                    int(window or 0), ctypes.c_float(scale), ctypes.c_float(cap), int(bool(precise_weights)),
+                    int(chunk or 0), _p(sinks), col0, dv, col0, _p(error_word(q.device)), _stream())
+                _ok(rc, "prefill_attention_mma_shared")
+            return
+        v_cache = k_cache
+    if not shared_values and dv == head_dim and decode_uses_tensor_cores(q.dtype, num_heads, num_kv_heads, head_dim, page_size):
         if k_cache.shape[1] != num_kv_heads or k_cache.shape[2] != page_size:
             raise KernelError("the cache must be [pages + 1, kv_heads, page_size, head_dim]")
         box_rows = min(page_size, 32)
@@ -336,14 +354,14 @@ def prefill_attention(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefi
             _p(q), kv_tensor_map(k_cache, box_rows), kv_tensor_map(v_cache, box_rows), _p(out), _p(block_table),
             block_table.shape[-1], _p(cu_q), _p(kv_len), _p(prefix_len), _p(rows), n_rows, max_q_len, num_heads,
             num_kv_heads, page_size, int(window or 0), ctypes.c_float(scale), ctypes.c_float(cap),
-            int(bool(precise_weights)), int(chunk or 0), _p(sinks), _p(error_word(q.device)), _stream())
+            int(bool(precise_weights)), int(chunk or 0), _p(sinks), 0, 0, 0, _p(error_word(q.device)), _stream())
         _ok(rc, "prefill_attention_mma")
         return
     rc = _attention(max(head_dim, dv)).b200_prefill_attention(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(block_table), block_table.shape[-1], _p(cu_q),
         _p(kv_len), _p(prefix_len), _p(rows), n_rows, max_q_len, num_heads, num_kv_heads, page_size,
         int(window or 0), ctypes.c_float(scale), _code(q), head_dim, dv, ctypes.c_float(cap), int(chunk or 0),
-        _p(sinks), _stream())
+        _p(sinks), head_dim if shared_values else 0, _stream())
     _ok(rc, "prefill_attention")
 
 
@@ -356,8 +374,30 @@ MMA_MAX_GROUP = 16
 MMA_MAX_HEAD_DIM = 256
 
 
-def _attention_mma(head_dim: int):
+def _attention_mma(head_dim: int, shared_value_tile: Optional[int] = None):
+    """The tensor-core attention library for a head size; ``shared_value_tile``: the form whose values are a range of
+    that many columns of the key rows."""
+    if shared_value_tile:
+        return load_cuda_library("attention_mma.cu", {"HEAD_DIM": head_dim, "V_DIM": shared_value_tile, "V_SHARED": 1})
     return load_cuda_library("attention_mma.cu", {"HEAD_DIM": head_dim})
+
+
+def shared_value_tile(value_dim: int) -> int:
+    """Columns of the values that one launch of the shared-row tensor-core kernels takes: the largest multiple of 16 up
+    to 256 that divides ``value_dim`` (0: none)."""
+    return next((t for t in range(256, 15, -16) if value_dim % t == 0), 0)
+
+
+def latent_head_group(num_heads: int) -> int:
+    """Query heads that one CTA of the shared-row kernels serves: the largest divisor of ``num_heads`` up to 16."""
+    return next(g for g in range(min(MMA_MAX_GROUP, num_heads), 0, -1) if num_heads % g == 0)
+
+
+def latent_uses_tensor_cores(dtype: torch.dtype, num_heads: int, key_dim: int, value_dim: int, page_size: int) -> bool:
+    """bfloat16 key rows of a multiple of 16 up to 512 columns whose leading ``value_dim`` columns are the values, cut
+    into tiles of a multiple of 16, pages of a power of two."""
+    return (dtype == torch.bfloat16 and key_dim % 16 == 0 and key_dim <= 512 and value_dim <= key_dim
+            and shared_value_tile(value_dim) > 0 and page_size > 0 and page_size & (page_size - 1) == 0)
 
 
 def decode_uses_tensor_cores(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int,
@@ -372,7 +412,7 @@ def decode_uses_tensor_cores(dtype: torch.dtype, num_heads: int, num_kv_heads: i
 _kv_maps = {}
 
 
-def kv_tensor_map(cache: torch.Tensor, box_rows: int):
+def kv_tensor_map(cache: torch.Tensor, box_rows: int, lib=None):
     """The 128-byte TMA descriptor of a cache tensor [pages + 1, kv_heads, page_size, head_dim] (made once)."""
     key = (cache.data_ptr(), tuple(cache.shape), box_rows)
     buf = _kv_maps.get(key)
@@ -381,7 +421,7 @@ def kv_tensor_map(cache: torch.Tensor, box_rows: int):
             raise KernelError("a TMA descriptor needs a contiguous bfloat16 cache [pages + 1, kv_heads, page_size, head_dim]")
         buf = ctypes.create_string_buffer(128)
         rows = cache.shape[0] * cache.shape[1] * cache.shape[2]
-        rc = _attention_mma(cache.shape[3]).b200_kv_tensor_map(buf, _p(cache), ctypes.c_longlong(rows), box_rows)
+        rc = (lib or _attention_mma(cache.shape[3])).b200_kv_tensor_map(buf, _p(cache), ctypes.c_longlong(rows), box_rows)
         if rc != 0:
             raise KernelError(f"the TMA descriptor of a cache tensor could not be made (code {rc})")
         if len(_kv_maps) > 4096:
@@ -407,9 +447,10 @@ def decode_scratch_floats(n_rows: int, num_heads: int, head_dim: int, splits: in
 def decode_attention(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_len, rows, n_rows,
                      num_heads, num_kv_heads, head_dim, page_size, window, scale, splits,
                      v_head_dim: Optional[int] = None, softcap: float = 0.0, precise_weights: bool = False,
-                     chunk: Optional[int] = None, sinks: Optional[torch.Tensor] = None) -> None:
+                     chunk: Optional[int] = None, sinks: Optional[torch.Tensor] = None,
+                     shared_values: bool = False) -> None:
     """Attention of single decoded tokens, the keys split over ``splits`` blocks per row (``v_head_dim``,
-    ``softcap``, ``precise_weights``, ``chunk``, ``sinks``: see ``prefill_attention``)."""
+    ``softcap``, ``precise_weights``, ``chunk``, ``sinks``, ``shared_values``: see ``prefill_attention``)."""
     _cuda(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_len, rows, sinks)
     _contig(q, k_cache, v_cache, out, block_table, scratch, sinks)
     _check_sinks(sinks, num_heads)
@@ -418,10 +459,28 @@ def decode_attention(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_le
     if k_cache.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelError("q, cache and output must share a dtype")
     dv = int(v_head_dim or head_dim)
-    plain = dv == head_dim
+    plain = dv == head_dim and not shared_values
     need = decode_scratch_floats(n_rows, num_heads, max(head_dim, dv), splits)
     if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
         raise KernelError(f"decode attention needs {need} floats of scratch")
+    if shared_values:
+        if num_kv_heads != 1 or k_cache.shape[1] != 1:
+            raise KernelError("values that are columns of the key rows need one KV head")
+        if latent_uses_tensor_cores(q.dtype, num_heads, head_dim, dv, page_size):
+            tile, group = shared_value_tile(dv), latent_head_group(num_heads)
+            lib = _attention_mma(head_dim, tile)
+            kmap = kv_tensor_map(k_cache, min(page_size, 32), lib)
+            groups = num_heads // group
+            in_kernel = splits == 1 or (splits in (2, 4, 8) and splits * groups * n_rows <= _sm_count(q.device))
+            for col0 in range(0, dv, tile):
+                rc = lib.b200_decode_attention_mma(
+                    _p(q), kmap, kmap, _p(out), _p(scratch), _p(block_table), block_table.shape[-1], _p(cu_q),
+                    _p(kv_len), _p(rows), n_rows, num_heads, groups, page_size, int(window or 0),
+                    ctypes.c_float(scale), splits, ctypes.c_float(softcap or 0.0), int(bool(precise_weights)),
+                    int(chunk or 0), _p(sinks), col0, dv, col0, _p(error_word(q.device)), _stream())
+                _ok(rc, "decode_attention_mma_shared", 1 if in_kernel else 2)
+            return
+        v_cache = k_cache
     if plain and decode_uses_tensor_cores(q.dtype, num_heads, num_kv_heads, head_dim, page_size):
         if k_cache.shape[1] != num_kv_heads or k_cache.shape[2] != page_size:
             raise KernelError("the cache must be [pages + 1, kv_heads, page_size, head_dim]")
@@ -430,7 +489,7 @@ def decode_attention(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_le
             _p(q), kv_tensor_map(k_cache, box_rows), kv_tensor_map(v_cache, box_rows), _p(out), _p(scratch), _p(block_table), block_table.shape[-1],
             _p(cu_q), _p(kv_len), _p(rows), n_rows, num_heads, num_kv_heads, page_size, int(window or 0),
             ctypes.c_float(scale), splits, ctypes.c_float(softcap or 0.0), int(bool(precise_weights)),
-            int(chunk or 0), _p(sinks), _p(error_word(q.device)), _stream())
+            int(chunk or 0), _p(sinks), 0, 0, 0, _p(error_word(q.device)), _stream())
         in_kernel = splits == 1 or (splits in (2, 4, 8) and splits * num_kv_heads * n_rows <= _sm_count(q.device))
         _ok(rc, "decode_attention_mma", 1 if in_kernel else 2)      # (a cluster of 2, 4 or 8 splits combines them itself)
         return
@@ -438,7 +497,7 @@ def decode_attention(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_le
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(scratch), _p(block_table), block_table.shape[-1],
         _p(cu_q), _p(kv_len), _p(rows), n_rows, num_heads, num_kv_heads, page_size, int(window or 0),
         ctypes.c_float(scale), splits, _code(q), head_dim, dv, ctypes.c_float(softcap or 0.0), int(chunk or 0),
-        _p(sinks), _stream())
+        _p(sinks), head_dim if shared_values else 0, _stream())
     _ok(rc, "decode_attention", 2 if splits > 1 else 1)
 
 
@@ -1638,12 +1697,12 @@ def heads_prepare(x: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor, v
 
 
 def latent_prepare(x: torch.Tensor, q_lat: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor,
-                   v_cache: torch.Tensor, latent_weight: torch.Tensor, eps: float, positions: torch.Tensor,
+                   v_cache: Optional[torch.Tensor], latent_weight: torch.Tensor, eps: float, positions: torch.Tensor,
                    slots: Optional[torch.Tensor], num_heads: int, head_dim: int, rot_dim: int, latent_dim: int,
                    inv_freq: Optional[torch.Tensor] = None, rot_dims: int = 0, interleaved: bool = True) -> None:
     """``x`` holds per head [head_dim plain | rot_dim rotated] query coordinates, then [latent_dim | rot_dim] of the
     down projection.  The latent is RMS-normed (``latent_weight``) and stored with the rotated key part behind it as
-    the token's one key [latent_dim + rot_dim] and alone as its value; the query that meets such keys is
+    the token's one key [latent_dim + rot_dim] and, if a value cache is given, alone as its value; the query that meets such keys is
     [q_lat[h, t] | rotated part] and goes to ``q_out`` [tokens, heads * (latent_dim + rot_dim)]."""
     _cuda(x, q_lat, q_out, k_cache, v_cache, latent_weight, positions, slots, inv_freq)
     _contig(x, q_lat, q_out, k_cache, v_cache, latent_weight, positions, slots, inv_freq)
@@ -1651,10 +1710,11 @@ def latent_prepare(x: torch.Tensor, q_lat: torch.Tensor, q_out: torch.Tensor, k_
     tokens = x.shape[0]
     if x.shape[1] < num_heads * (head_dim + rot_dim) + latent_dim + rot_dim or \
             tuple(q_lat.shape) != (num_heads, tokens, latent_dim) or latent_weight.numel() != latent_dim or \
-            q_lat.dtype != x.dtype or q_out.dtype != x.dtype or k_cache.dtype != x.dtype or v_cache.dtype != x.dtype:
+            q_lat.dtype != x.dtype or q_out.dtype != x.dtype or k_cache.dtype != x.dtype or \
+            (v_cache is not None and v_cache.dtype != x.dtype):
         raise KernelError("latent_prepare: sizes or dtypes do not fit")
     if tuple(k_cache.shape[1:]) != (1, k_cache.shape[2], latent_dim + rot_dim) or \
-            tuple(v_cache.shape[1:]) != (1, k_cache.shape[2], latent_dim):
+            (v_cache is not None and tuple(v_cache.shape[1:]) != (1, k_cache.shape[2], latent_dim)):
         raise KernelError("the latent cache must be [pages + 1, 1, page_size, latent_dim + rot_dim] and [.., latent_dim]")
     if inv_freq is not None and inv_freq.numel() * 2 != rot_dims:
         raise KernelError("one frequency for every rotated pair is needed")

@@ -241,30 +241,36 @@ class GatedConvAttention(Part):
         return ops.linear(out, p["o_proj"])
 
 
-def _masked_attention(part, q, out, ctx, cache, num_heads, num_kv_heads, head_dim, v_head_dim, sinks):
+def _masked_attention(part, q, out, ctx, cache, num_heads, num_kv_heads, head_dim, v_head_dim, sinks,
+                      shared_values=False):
     """Attention of a step's rows over the paged cache for a mixer with ``window``, ``chunk`` and ``scale``: prompt
-    portions and single decoded tokens, softmax weights in float."""
+    portions and single decoded tokens, softmax weights in float.  ``shared_values``: a value is the first
+    ``v_head_dim`` columns of its key's row (one KV head)."""
     g = cache.group
     page = ctx.page_sizes[g]
     if ctx.num_prefill:
         ops.prefill_attention(q, cache.k, cache.v, out, ctx.block_tables[g], ctx.cu_q, ctx.kv_len,
                               ctx.prefix_len, ctx.prefill_rows, ctx.num_prefill, ctx.max_q_len,
                               num_heads, num_kv_heads, head_dim, page, part.window, part.scale,
-                              v_head_dim=v_head_dim, precise_weights=True, chunk=part.chunk, sinks=sinks)
+                              v_head_dim=v_head_dim, precise_weights=True, chunk=part.chunk, sinks=sinks,
+                              shared_values=shared_values)
     if ctx.num_decode:
         bound = ctx.kv_len_bound
         for limit in (part.window, part.chunk):
             if limit:
                 bound = min(bound, limit)
         plain = v_head_dim == head_dim
-        per_split = ops.decode_ctas_per_split(q.dtype, ctx.num_decode, num_heads, num_kv_heads, head_dim, page, plain)
+        if shared_values and ops.latent_uses_tensor_cores(q.dtype, num_heads, head_dim, v_head_dim, page):
+            per_split = ctx.num_decode * (num_heads // ops.latent_head_group(num_heads))
+        else:
+            per_split = ops.decode_ctas_per_split(q.dtype, ctx.num_decode, num_heads, num_kv_heads, head_dim, page, plain)
         splits = decode_splits(per_split, bound, ctx.sm_count)
         need = ops.decode_scratch_floats(ctx.num_decode, num_heads, max(head_dim, v_head_dim), splits)
         scratch = ctx.scratch(need) if need else None
         ops.decode_attention(q, cache.k, cache.v, out, scratch, ctx.block_tables[g], ctx.cu_q,
                              ctx.kv_len, ctx.decode_rows, ctx.num_decode, num_heads, num_kv_heads, head_dim,
                              page, part.window, part.scale, splits, v_head_dim=v_head_dim, precise_weights=True,
-                             chunk=part.chunk, sinks=sinks)
+                             chunk=part.chunk, sinks=sinks, shared_values=shared_values)
 
 
 class GroupedAttention(Part):
@@ -362,8 +368,8 @@ class LatentAttention(Part):
 
         q_plain . (W_uk[h] c) = (W_uk[h]^T q_plain) . c,        sum_j p_j W_uv[h] c_j = W_uv[h] (sum_j p_j c_j)
 
-    so the cache holds ONE key per token, [c | k_rot] (kv_rank + rot_dim wide, one KV head for all query heads),
-    whose value is c; a head's query is [W_uk[h]^T q_plain | q_rot] and its output W_uv[h] times the attention's
+    so the cache holds ONE row per token, [c | k_rot] (kv_rank + rot_dim wide, one KV head for all query heads): it
+    is the token's key, and its first kv_rank columns are the token's value (no value tensor is kept); a head's query is [W_uk[h]^T q_plain | q_rot] and its output W_uv[h] times the attention's
     result.  ``window``, ``chunk``, ``sink``, ``gate``, ``position_encoding`` / ``rot_dims``: as in
     ``grouped_attention``."""
     category = "mixer"
@@ -411,7 +417,7 @@ class LatentAttention(Part):
             self.uk_t = tensor.view(self.nh, self.d, self.c).transpose(1, 2).contiguous()
 
     def cache_spec(self):
-        return PagedKVSpec(1, self.c + self.r, self.window, self.c)
+        return PagedKVSpec(1, self.c + self.r, self.window, self.c, shared_values=True)
 
     def state_spec(self):
         return None
@@ -431,7 +437,7 @@ class LatentAttention(Part):
                            rot_dims=self.rot_dims if rope else 0,
                            interleaved=getattr(rope, "pairing", "half_split") == "interleaved")
         o_lat = torch.empty((tokens, self.nh * self.c), dtype=packed.dtype, device=packed.device)
-        _masked_attention(self, q, o_lat, ctx, cache, self.nh, 1, width, self.c, p.get("sink"))
+        _masked_attention(self, q, o_lat, ctx, cache, self.nh, 1, width, self.c, p.get("sink"), shared_values=True)
         out = torch.empty((tokens, self.nh * self.dv), dtype=packed.dtype, device=packed.device)
         ops.head_products(o_lat.view(tokens, self.nh, self.c).transpose(0, 1),
                           p["uv_proj"].view(self.nh, self.dv, self.c),

@@ -49,6 +49,9 @@ class PagedKVSpec:
     head_dim: int
     window: Optional[int] = None     # None: all keys are kept; W: only the last W positions are read
     v_head_dim: Optional[int] = None  # width of a value where it differs from a key's (None: head_dim)
+    # A value is the first v_head_dim columns of its key's row: no value tensor is kept, and attention reads both out
+    # of the key rows (a latent that is key and value at once).
+    shared_values: bool = False
 
 
 @dataclass(frozen=True)

@@ -116,20 +116,22 @@ def test_experts_chosen_by_a_table(tokens, width, ff, experts, top, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_activations_joint_norm_with_gate_and_cap(dtype):
+@pytest.mark.parametrize("width", [70, 72])            # rows of odd size, and rows of whole 16-byte pieces (eight a thread)
+def test_activations_joint_norm_with_gate_and_cap(dtype, width):
     from llm_infer_rust_b200.kernels import ops
     dev = torch.device("cuda")
     g = torch.Generator().manual_seed(2)
-    z = (torch.randn(5, 70, generator=g) * 3).to(dtype)
+    z = (torch.randn(5, width, generator=g) * 3).to(dtype)
     tol = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=1e-2, atol=1e-2)
     zd = z.double()
     tanh_form = 0.5 * zd * (1 + torch.tanh(math.sqrt(2 / math.pi) * (zd + 0.044715 * zd ** 3)))
     for act, want in (("silu", P.silu(zd)), ("gelu_erf", P.gelu_erf(zd)), ("gelu_tanh", tanh_form)):
         torch.testing.assert_close(ops.activate(z.to(dev), act).cpu().double(), want, **tol)
-    part = z.to(dev).clone()
-    ops.activate(part, "silu", columns=33, in_place=True)                     # the first columns only, in place
-    torch.testing.assert_close(part[:, :33].cpu().double(), P.silu(zd[:, :33]), **tol)
-    assert torch.equal(part[:, 33:].cpu(), z[:, 33:])
+    for columns in (33, 40):                                                  # the first columns only, in place
+        part = z.to(dev).clone()
+        ops.activate(part, "silu", columns=columns, in_place=True)
+        torch.testing.assert_close(part[:, :columns].cpu().double(), P.silu(zd[:, :columns]), **tol)
+        assert torch.equal(part[:, columns:].cpu(), z[:, columns:])
     o = torch.randn(5, 30, generator=g) * 4
     wn = 1 + 0.2 * torch.randn(30, generator=g)
     want = P.rms_norm(o.double(), wn.double(), 1e-5, one_plus=False) * P.sigmoid(zd[:, 40:70])
@@ -213,6 +215,52 @@ def test_keys_that_stand_out_just_inside_and_just_outside_an_edge(mask, size, d,
     want = P.masked_softmax_attention(q.double(), k.double().repeat_interleave(rep, 1), v.double().repeat_interleave(rep, 1),
                                       0.7, visible)
     torch.testing.assert_close(no_sink.double(), want, rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,dk,dv", [(6, 80, 64), (3, 14, 10), (32, 320, 256), (40, 96, 48), (4, 448, 384)])
+def test_values_that_are_columns_of_the_key_rows(H, dk, dv, dtype):
+    """One row a token that is every head's key and whose first columns are its value (a latent): no value cache.
+    Widths that take the all-sizes kernel and widths that take the tensor-core kernels (one and several column tiles
+    of the values, more heads than one CTA serves), a window, sinks, prompt portions and decoded tokens."""
+    from llm_infer_rust_b200.kernels import ops
+    dev = torch.device("cuda")
+    g = torch.Generator().manual_seed(H + dk)
+    T, page, window, scale = 150, 16, 37, 1.0 / math.sqrt(dk)
+    q = M.bf16_values(torch.randn(T, H, dk, generator=g))
+    k = M.bf16_values(torch.randn(T, 1, dk, generator=g))
+    sinks = torch.randn(H, generator=g)
+    for i in (60, 100, 149):                                                  # a key at the window's edges that fits the query
+        k[i - window] = M.bf16_values(8.0 * q[i, 0:1] / q[i, 0].norm())
+        k[i - window + 1] = M.bf16_values(5.0 * q[i, 0:1] / q[i, 0].norm())
+    want = P.masked_softmax_attention(q.double(), k.double().expand(T, H, dk), k.double()[..., :dv].expand(T, H, dv),
+                                      scale, P.window_mask(T, window), sink=sinks.double())
+    pages = -(-T // page)
+    order = torch.randperm(pages, generator=torch.Generator().manual_seed(3)) + 1
+    k_cache = torch.full((pages + 1, 1, page, dk), 55.0, device=dev, dtype=dtype)
+    table = order.to(torch.int32).reshape(1, -1).to(dev)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    got, at = [], 0
+    for n in [70, 2, 33, 1, 1, 1, 20] + [1] * 22:
+        for p_ in range(at, at + n):
+            k_cache[int(order[p_ // page]), 0, p_ % page] = k[p_, 0].to(dev, dtype)
+        qo = q[at:at + n].reshape(n, -1).to(dev, dtype).contiguous()
+        o = torch.empty((n, H * dv), device=dev, dtype=dtype)
+        args = (table, i32([0, n]), i32([at + n]))
+        if n > 1:
+            ops.prefill_attention(qo, k_cache, None, o, *args, i32([at]), i32([0]), 1, n, H, 1, dk, page, window, scale,
+                                  v_head_dim=dv, precise_weights=True, sinks=sinks.to(dev), shared_values=True)
+        else:
+            splits = 1 if at <= 110 else (2 if at <= 130 else 3)
+            scratch = torch.empty(max(ops.decode_scratch_floats(1, H, dk, splits), 1), device=dev)
+            ops.decode_attention(qo, k_cache, None, o, scratch, *args, i32([0]), 1, H, 1, dk, page, window, scale,
+                                 splits, v_head_dim=dv, precise_weights=True, sinks=sinks.to(dev), shared_values=True)
+        got.append(o.cpu().float().reshape(n, H, dv))
+        at += n
+    assert at == T
+    ops.check_errors(dev)
+    tol = 2e-5 if dtype == torch.float32 else 3e-2
+    torch.testing.assert_close(torch.cat(got).double(), want, rtol=tol, atol=tol)
 
 
 # ----------------------------------------------------------------------------- models
