@@ -571,7 +571,6 @@ def mukenex_kernel_table(size, peak):
         lq = nh * (d + r)
         lpacked = (torch.randn(T, lq + rank + r, device=dev) * 0.5).to(bf)
         lk = torch.zeros(c.pages, 1, page, rank + r, dtype=bf, device=dev).normal_()
-        lv = torch.zeros(c.pages, 1, page, rank, dtype=bf, device=dev).normal_()
         uk_t = (torch.randn(nh, rank, d, device=dev) * d ** -0.5).to(bf)
         uv = (torch.randn(nh, d, rank, device=dev) * rank ** -0.5).to(bf)
         q_plain = lpacked[:, :lq].view(T, nh, d + r)[:, :, :d].transpose(0, 1)
@@ -582,8 +581,8 @@ def mukenex_kernel_table(size, peak):
         inv_freq = torch.pow(torch.tensor(1e6), -torch.arange(0, r, 2) / r).to(dev)
         lw = torch.ones(rank, device=dev)
         put(f"{phase}.mukenex.latent_prepare", timed_alone(lambda: ops.latent_prepare(
-            lpacked, q_lat, lqo, lk, lv, lw, 1e-5, c.positions, c.slots, nh, d, r, rank, inv_freq=inv_freq, rot_dims=r),
-            flush), T * (nh * (rank * 2 + r * 2) * 2 + (rank + r) * 2 * 2))
+            lpacked, q_lat, lqo, lk, None, lw, 1e-5, c.positions, c.slots, nh, d, r, rank, inv_freq=inv_freq, rot_dims=r),
+            flush), T * (nh * (rank * 2 + r * 2) * 2 + (rank + r) * 2 * 2))      # (the latent is stored once: key and value)
         # --- attention
         o = torch.empty(T, nh * d, dtype=bf, device=dev)
         lo = torch.empty(T, nh * rank, dtype=bf, device=dev)
@@ -594,8 +593,8 @@ def mukenex_kernel_table(size, peak):
                 d ** -0.5, v_head_dim=d, precise_weights=True, chunk=window), flush, repeats=3),
                 flops=4.0 * nh * d * seen(T, window, True), of="bf16")
             put("prefill.mukenex.attention_latent", timed_alone(lambda: ops.prefill_attention(
-                lqo, lk, lv, lo, c.table, c.cu_q, c.kv_len, c.prefix_len, c.rows, 1, T, nh, 1, rank + r, page, window,
-                (d + r) ** -0.5, v_head_dim=rank, precise_weights=True, sinks=sinks), flush, repeats=3),
+                lqo, lk, None, lo, c.table, c.cu_q, c.kv_len, c.prefix_len, c.rows, 1, T, nh, 1, rank + r, page, window,
+                (d + r) ** -0.5, v_head_dim=rank, precise_weights=True, sinks=sinks, shared_values=True), flush, repeats=3),
                 flops=2.0 * nh * (2 * rank + r) * seen(T, window, False), of="bf16")
             put("prefill.qwen3.attention", timed_alone(lambda: ops.prefill_attention(
                 q, k_cache, v_cache, o, c.table, c.cu_q, c.kv_len, c.prefix_len, c.rows, 1, T, nh, nkv, d, page, None,
@@ -603,7 +602,10 @@ def mukenex_kernel_table(size, peak):
         else:
             def decode(name, qq, kk, vv, oo, heads, kvh, dk, dv_, bound, nbytes, **kw):
                 plain = dk == dv_
-                splits = decode_splits(ops.decode_ctas_per_split(bf, rows_dec, heads, kvh, dk, page, plain), bound, 148)
+                per_split = ops.decode_ctas_per_split(bf, rows_dec, heads, kvh, dk, page, plain)
+                if kw.get("shared_values"):
+                    per_split = rows_dec * (heads // ops.latent_head_group(heads))
+                splits = decode_splits(per_split, bound, 148)
                 need = ops.decode_scratch_floats(rows_dec, heads, max(dk, dv_), splits)
                 scratch = torch.empty(max(need, 1), device=dev)
                 win, scale = kw.pop("window_", None), kw.pop("scale_", dk ** -0.5)
@@ -613,9 +615,9 @@ def mukenex_kernel_table(size, peak):
             kv_all = rows_dec * ctx_len * nkv * d * 2 * 2
             decode("decode.mukenex.attention_blocks", q, k_cache, v_cache, o, nh, nkv, d, d, window,
                    rows_dec * window * nkv * d * 2 * 2, v_head_dim=d, precise_weights=True, chunk=window)
-            decode("decode.mukenex.attention_latent", lqo, lk, lv, lo, nh, 1, rank + r, rank, window,
-                   rows_dec * window * (2 * rank + r) * 2, v_head_dim=rank, precise_weights=True, sinks=sinks,
-                   window_=window)
+            decode("decode.mukenex.attention_latent", lqo, lk, None, lo, nh, 1, rank + r, rank, window,
+                   rows_dec * window * (rank + r) * 2, v_head_dim=rank, precise_weights=True, sinks=sinks,
+                   window_=window, shared_values=True)
             decode("decode.qwen3.attention", q, k_cache, v_cache, o, nh, nkv, d, d, ctx_len, kv_all)
         lo_t = lo.view(T, nh, rank).transpose(0, 1)
         lout = torch.empty(T, nh * d, dtype=bf, device=dev)

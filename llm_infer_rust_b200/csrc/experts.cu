@@ -147,7 +147,9 @@ expert_gemm_f32_kernel(const float* __restrict__ A, int lda, const int* __restri
 
 // ------------------------------------------------------------------ bfloat16 products on tensor cores
 // The same tiles; 8 warps, warp w owns rows 16 * (w / 2) .. and columns 32 * (w % 2) .. of the tile (two 16 x 16
-// accumulators, four when GATED); k in steps of 32 through shared memory.  TO: bfloat16 (H) or float (Y).
+// accumulators, four when GATED); k in steps of 64 through shared memory, the next step's operands fetched into
+// registers while the tensor cores work on this one (a decode step's products are a chain of such fetches: few rows
+// an expert, all of its weights).  TO: bfloat16 (H) or float (Y).
 template <bool GATED, typename TO>
 __global__ void __launch_bounds__(256)
 expert_gemm_bf16_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int* __restrict__ gather,
@@ -156,7 +158,7 @@ expert_gemm_bf16_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int*
                         const int* __restrict__ tile_expert, const int* __restrict__ tile_first,
                         const int* __restrict__ num_tiles) {
   using namespace nvcuda;
-  constexpr int BK = 32, LD = BK + 8, G = GATED ? 2 : 1;
+  constexpr int BK = 64, LD = BK + 8, G = GATED ? 2 : 1;
   if (static_cast<int>(blockIdx.y) >= *num_tiles) return;
   __shared__ __align__(32) __nv_bfloat16 As[TM][LD];
   __shared__ __align__(32) __nv_bfloat16 Ws[G][TN][LD];
@@ -167,12 +169,15 @@ expert_gemm_bf16_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int*
   const __nv_bfloat16* We = W + e * w_expert_stride;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int wr = warp >> 1, wc = warp & 1;
-  // loads: thread -> row tid / 4, eight k from (tid % 4) * 8
-  const int lrow = tid >> 2, lk = (tid & 3) * 8;
+  // loads: thread -> row tid / 4, sixteen k from (tid % 4) * 16, as two pieces of eight
+  const int lrow = tid >> 2, lk = (tid & 3) * 16;
   const int arow = r0 + lrow;
   const __nv_bfloat16* a_src = nullptr;
   if (arow < r_end) a_src = A + static_cast<size_t>(gather ? gather[arow] : arow) * lda;
   const int wn = n0 + lrow;
+  const __nv_bfloat16* w_src[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) w_src[g] = wn < N ? We + static_cast<size_t>(wn + g * up_row_offset) * K : nullptr;
   const bool vec = (K % 8 == 0) && (lda % 8 == 0) && (reinterpret_cast<uintptr_t>(A) % 16 == 0) &&
                    (reinterpret_cast<uintptr_t>(W) % 16 == 0);
   wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[G][2];
@@ -180,27 +185,41 @@ expert_gemm_bf16_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int*
   for (int g = 0; g < G; ++g)
 #pragma unroll
     for (int j = 0; j < 2; ++j) wmma::fill_fragment(acc[g][j], 0.0f);
-  const __nv_bfloat16 zero = __float2bfloat16_rn(0.0f);
+
+  // eight elements of a row from k on, zeros beyond K or for a row that does not exist
+  auto fetch8 = [&](const __nv_bfloat16* row, int k) -> uint4 {
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (row == nullptr || k >= K) return v;
+    if (vec && k + 8 <= K) return *reinterpret_cast<const uint4*>(row + k);
+    __align__(16) __nv_bfloat16 t[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t[i] = k + i < K ? row[k + i] : __float2bfloat16_rn(0.0f);
+    return *reinterpret_cast<const uint4*>(t);
+  };
+  uint4 ra[2], rw[G][2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    ra[h] = fetch8(a_src, lk + 8 * h);
+#pragma unroll
+    for (int g = 0; g < G; ++g) rw[g][h] = fetch8(w_src[g], lk + 8 * h);
+  }
   for (int k0 = 0; k0 < K; k0 += BK) {
-    __syncthreads();
-    const int kk = k0 + lk;
-    if (vec && kk + 8 <= K) {
-      uint4 z = make_uint4(0, 0, 0, 0);
-      *reinterpret_cast<uint4*>(&As[lrow][lk]) = a_src ? *reinterpret_cast<const uint4*>(a_src + kk) : z;
+    __syncthreads();                                   // the step before is no longer read
 #pragma unroll
-      for (int g = 0; g < G; ++g)
-        *reinterpret_cast<uint4*>(&Ws[g][lrow][lk]) =
-            wn < N ? *reinterpret_cast<const uint4*>(We + static_cast<size_t>(wn + g * up_row_offset) * K + kk) : z;
-    } else {
+    for (int h = 0; h < 2; ++h) {
+      *reinterpret_cast<uint4*>(&As[lrow][lk + 8 * h]) = ra[h];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        As[lrow][lk + i] = (a_src && kk + i < K) ? a_src[kk + i] : zero;
-#pragma unroll
-        for (int g = 0; g < G; ++g)
-          Ws[g][lrow][lk + i] = (wn < N && kk + i < K) ? We[static_cast<size_t>(wn + g * up_row_offset) * K + kk + i] : zero;
-      }
+      for (int g = 0; g < G; ++g) *reinterpret_cast<uint4*>(&Ws[g][lrow][lk + 8 * h]) = rw[g][h];
     }
     __syncthreads();
+    if (k0 + BK < K) {                                 // the next step's operands are on their way during the products
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        ra[h] = fetch8(a_src, k0 + BK + lk + 8 * h);
+#pragma unroll
+        for (int g = 0; g < G; ++g) rw[g][h] = fetch8(w_src[g], k0 + BK + lk + 8 * h);
+      }
+    }
 #pragma unroll
     for (int ks = 0; ks < BK; ks += 16) {
       wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> fa;
