@@ -281,6 +281,66 @@ def test_whole_decoded_and_in_portions(name, dtype, models):
     assert eng.cache.manager.check() == ""
 
 
+def drawn_config(seed):
+    """A configuration whose every size, option and layer order is drawn: any model of the design must run as it is."""
+    import random
+    rng = random.Random(seed)
+    even = lambda lo, hi: 2 * rng.randint(lo // 2, hi // 2)
+
+    def feed_forward():
+        kind = rng.choice(["none", "dense", "moe", "moe"])
+        if kind == "none":
+            return None
+        if kind == "dense":
+            return M.dense(rng.randint(8, 64))
+        experts = rng.randint(2, 6)
+        return M.moe(rng.randint(8, 40), experts, rng.randint(1, experts))
+
+    layers = []
+    for _ in range(rng.randint(2, 5)):
+        kind = rng.choice(["latent", "attention", "lightning"])
+        if kind == "latent":
+            tensor_cores = rng.random() < 0.4                 # widths that the tensor-core kernels take, and others
+            rot_dim = rng.choice([16, 32]) if tensor_cores else even(2, 16)
+            rank = rng.choice([16, 32, 48]) if tensor_cores else even(4, 40)
+            layers.append(M.latent(rng.randint(1, 8), even(4, 24), rot_dim, rng.randint(2, 24), rank,
+                                   rng.uniform(0.1, 0.6), rng.randint(3, 70), base=rng.choice([50.0, 1000.0, 20000.0]),
+                                   dims=even(2, rot_dim), mlp=feed_forward()))
+        elif kind == "attention":
+            kv = rng.randint(1, 3)
+            dim = rng.choice([16, 32]) if rng.random() < 0.4 else even(4, 40)
+            vdim = dim if rng.random() < 0.5 else even(4, 40)
+            layers.append(M.attention(kv * rng.randint(1, 4), kv, dim, vdim, rng.uniform(0.1, 0.6), rng.randint(3, 70),
+                                      mlp=feed_forward()))
+        else:
+            heads = rng.randint(1, 3)
+            layers.append(M.lightning(heads, even(4, 40), even(4, 40), [rng.uniform(0.5, 0.999) for _ in range(heads)],
+                                      mlp=feed_forward()))
+    loop = None
+    if rng.random() < 0.6:
+        start = rng.randint(0, len(layers) - 1)
+        loop = (start, rng.randint(start, len(layers)), rng.randint(1, 3))
+    return M.config(rng.randint(50, 300), even(24, 96), rng.choice([1e-5, 1e-6, 3e-4]), layers,
+                    streams=rng.choice([None, 1, 2, 3, 4, 5]), loop=loop, softcap=rng.choice([None, 8.0, 40.0]))
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_configurations_drawn_at_random(seed, tmp_path):
+    raw = drawn_config(seed)
+    w = M.random_weights(raw, 300 + seed)
+    folder = M.write_model(str(tmp_path / "m"), raw, w)
+    T = 90
+    ids = M.tokens(raw["vocab"], T, seed)
+    want = M.oracle(raw, w, ids)
+    for dtype in ("float32", "bfloat16"):
+        eng = M.make_engine(folder, dtype, page_size=(4, 8, 16)[seed % 3], pool_tokens=256)
+        M.check(M.run_alone(eng, 1, ids, [T]), want, dtype, f"{seed} whole")
+        M.check(M.run_alone(eng, 2, ids, [T - 30] + [1] * 30), want, dtype, f"{seed} last 30 decoded")
+        M.check(M.run_alone(eng, 3, ids, cut(T, [2, 17, 3, 40, 1, 5])), want, dtype, f"{seed} in portions")
+        assert eng.cache.manager.check() == ""
+        del eng
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_far_keys_with_sharp_scores_and_slow_decays(dtype, models):
     """Prompts of hundreds of tokens over many pages; scores so sharp that the best key inside the window or block,
